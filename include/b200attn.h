@@ -1,0 +1,142 @@
+/*
+ * b200attn — C ABI of the B200 (sm_100a) attention engine.
+ *
+ * This is the drop-in boundary for the attention path of min_fa3_demo: every
+ * entry point takes plain device pointers, sizes and a CUDA stream handle, and
+ * replaces one host binding of the reference (cited per function, paths relative
+ * to the reference project).  The library allocates no device memory: outputs
+ * and scratch ("workspace") are owned by the caller; b2a_*_workspace_bytes()
+ * says how much scratch a call needs.  All functions return 0 on success and a
+ * negative B2A_ERR_* code on failure; b2a_last_error() returns a thread-local
+ * description of the last failure.  Nothing here throws or exits.
+ *
+ * Tensors are bf16, head_dim = 128, laid out as a flat [tokens, heads, 128]
+ * array.  A fixed-length BSHD batch is the special case tokens = batch * seqlen
+ * with cu_seqlens == NULL.  Launches are asynchronous on the given stream.
+ */
+#ifndef B200ATTN_H_
+#define B200ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2A_OK 0
+#define B2A_ERR_INVALID_ARGUMENT (-1)
+#define B2A_ERR_CUDA (-2)
+#define B2A_ERR_WORKSPACE_TOO_SMALL (-3)
+#define B2A_ERR_UNSUPPORTED_DEVICE (-4)
+#define B2A_ERR_DEVICE_STATUS (-5)
+
+/* Version of this ABI (bumped when a struct layout changes). */
+int b2a_abi_version(void);
+
+/* Thread-local text of the last error returned on this thread ("" if none). */
+const char* b2a_last_error(void);
+
+/* ------------------------------------------------------------------------- */
+/* Forward                                                                    */
+/* ------------------------------------------------------------------------- */
+
+typedef struct b2a_fwd_args {
+    const void* q;              /* bf16 [total_q, heads_q, 128] */
+    const void* k;              /* bf16 [total_k, heads_k, 128] */
+    const void* v;              /* bf16 [total_k, heads_k, 128] */
+    void* out;                  /* bf16 [total_q, heads_q, 128] */
+    float* lse;                 /* BSHD: [batch, heads_q, seqlen_q]; varlen: [heads_q, total_q] */
+    const int32_t* cu_seqlens_q; /* device int32 [batch + 1], NULL for BSHD */
+    const int32_t* cu_seqlens_k; /* device int32 [batch + 1], NULL for BSHD */
+    int32_t batch;
+    int32_t seqlen_q;           /* BSHD: S_q.  varlen: max_seqlen_q */
+    int32_t seqlen_k;           /* BSHD: S_k.  varlen: max_seqlen_k */
+    int32_t total_q;            /* tokens in q (batch * seqlen_q for BSHD) */
+    int32_t total_k;
+    int32_t heads_q;
+    int32_t heads_k;
+    int32_t head_dim;           /* must be 128 */
+    int32_t is_causal;          /* bottom-right aligned causal mask */
+    int32_t merge_running;      /* 1: merge into the partial result already in out/lse */
+    int32_t grid_blocks;        /* 0 = one CTA per SM; >0 overrides the CTA count */
+    float softmax_scale;        /* 0 = 1/sqrt(head_dim) */
+    void* workspace;            /* device scratch, 16-byte aligned */
+    size_t workspace_bytes;
+} b2a_fwd_args;
+
+/* Scratch needed by b2a_fwd for these sizes. */
+size_t b2a_fwd_workspace_bytes(int32_t batch, int32_t total_q, int32_t is_varlen);
+
+/*
+ * Attention forward: out = softmax(scale * q k^T [+causal]) v, lse = logsumexp.
+ * Replaces `forward` (bindings.cpp:240) and `forward_varlen` (bindings.cpp:280)
+ * of the reference, including its varlen scheduler-metadata kernel
+ * (csrc/min_fa3_varlen_prepare_scheduler.cu:214); with merge_running = 1 it is
+ * the compute half of `forward_varlen_ring`
+ * (csrc/min_fa3_varlen_ring_bindings.cu:231).
+ */
+int b2a_fwd(const b2a_fwd_args* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------- */
+/* Backward                                                                   */
+/* ------------------------------------------------------------------------- */
+
+typedef struct b2a_bwd_args {
+    const void* dout;           /* bf16 [total_q, heads_q, 128] */
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* out;            /* forward output */
+    const float* lse;           /* forward LSE (layout as in b2a_fwd_args) */
+    void* dq;                   /* bf16 [total_q, heads_q, 128] */
+    void* dk;                   /* bf16 [total_k, heads_k, 128] */
+    void* dv;                   /* bf16 [total_k, heads_k, 128] */
+    const int32_t* cu_seqlens_q;
+    const int32_t* cu_seqlens_k;
+    int32_t batch;
+    int32_t seqlen_q;
+    int32_t seqlen_k;
+    int32_t total_q;
+    int32_t total_k;
+    int32_t heads_q;
+    int32_t heads_k;
+    int32_t head_dim;
+    int32_t is_causal;
+    int32_t deterministic;      /* 1: bitwise repeatable dq accumulation order */
+    int32_t grid_blocks;
+    float softmax_scale;
+    void* workspace;
+    size_t workspace_bytes;
+} b2a_bwd_args;
+
+size_t b2a_bwd_workspace_bytes(int32_t batch, int32_t total_q, int32_t total_k, int32_t heads_q,
+                               int32_t heads_k, int32_t is_varlen);
+
+/*
+ * Attention backward: dq, dk, dv from dout and the forward's q, k, v, out, lse.
+ * Replaces `backward` (csrc/backward/min_fa3_bwd_bindings.cu:156) and
+ * `backward_varlen` (csrc/backward/min_fa3_bwd_bindings.cu:255): the dO*O
+ * preprocess, the dK/dV main loop that recomputes P from LSE, fp32 dQ
+ * accumulation and the cast back to bf16.
+ */
+int b2a_bwd(const b2a_bwd_args* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------- */
+/* Device status                                                              */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Synchronises the stream and reads the status word that kernels launched with
+ * this workspace wrote.  Returns B2A_OK, or B2A_ERR_DEVICE_STATUS with the
+ * decoded status in b2a_last_error() (for example a bounded wait that ran out).
+ * No counterpart in the reference, whose device-side waits are unbounded
+ * (include/mega_ring_semaphore.cuh:69-80).
+ */
+int b2a_check_status(const void* workspace, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200ATTN_H_ */

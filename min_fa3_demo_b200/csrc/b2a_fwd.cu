@@ -1,0 +1,144 @@
+// C-ABI entry point and launcher of the forward attention kernel.
+#include "b2a_fwd.cuh"
+#include "b2a_host.cuh"
+
+#include <cmath>
+
+namespace b2a {
+
+namespace {
+
+constexpr size_t kFwdSmemBytes = sizeof(FwdShared) + 1024;   // + slack for 1 KiB alignment
+
+template <bool kMerge>
+int configure_fwd_kernel(const DeviceInfo& dev) {
+    static bool done[64][2] = {};
+    if (!done[dev.device][kMerge ? 1 : 0]) {
+        if (static_cast<size_t>(dev.max_smem_optin) < kFwdSmemBytes) {
+            return fail(B2A_ERR_UNSUPPORTED_DEVICE, "device offers %d bytes of shared memory, need %zu",
+                        dev.max_smem_optin, kFwdSmemBytes);
+        }
+        B2A_CUDA_OK(cudaFuncSetAttribute(fwd_kernel<kMerge>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kFwdSmemBytes)));
+        done[dev.device][kMerge ? 1 : 0] = true;
+    }
+    return B2A_OK;
+}
+
+}  // namespace
+
+}  // namespace b2a
+
+extern "C" {
+
+size_t b2a_fwd_workspace_bytes(int32_t batch, int32_t total_q, int32_t is_varlen) {
+    size_t bytes = sizeof(b2a::WorkspaceHeader);
+    if (is_varlen) {
+        bytes += b2a::max_entries(batch, total_q, b2a::kFwdRowsPerWork) * sizeof(int2);
+    }
+    return b2a::align_up(bytes, 256);
+}
+
+int b2a_fwd(const b2a_fwd_args* a, void* cuda_stream) {
+    using namespace b2a;
+    B2A_REQUIRE(a != nullptr, "args must not be NULL");
+    B2A_REQUIRE(a->q && a->k && a->v && a->out && a->lse, "q, k, v, out and lse must not be NULL");
+    B2A_REQUIRE(a->head_dim == kHeadDim, "head_dim must be 128, got %d", a->head_dim);
+    B2A_REQUIRE(a->batch >= 1, "batch must be >= 1, got %d", a->batch);
+    B2A_REQUIRE(a->heads_q >= 1 && a->heads_k >= 1 && a->heads_q % a->heads_k == 0,
+                "heads_q %% heads_k must be 0, got heads_q=%d heads_k=%d", a->heads_q, a->heads_k);
+    B2A_REQUIRE(a->total_q >= 1 && a->total_k >= 1, "total_q and total_k must be positive");
+    B2A_REQUIRE((a->cu_seqlens_q == nullptr) == (a->cu_seqlens_k == nullptr),
+                "cu_seqlens_q and cu_seqlens_k must both be given or both be NULL");
+    const bool varlen = a->cu_seqlens_q != nullptr;
+    if (!varlen) {
+        B2A_REQUIRE(a->seqlen_q >= 1 && a->seqlen_k >= 1, "seqlen_q and seqlen_k must be positive");
+        B2A_REQUIRE(static_cast<long long>(a->batch) * a->seqlen_q == a->total_q &&
+                        static_cast<long long>(a->batch) * a->seqlen_k == a->total_k,
+                    "BSHD sizes must satisfy total = batch * seqlen");
+    }
+    B2A_REQUIRE(a->grid_blocks >= 0, "grid_blocks must be >= 0, got %d", a->grid_blocks);
+    B2A_REQUIRE(a->workspace != nullptr && (reinterpret_cast<uintptr_t>(a->workspace) & 0xF) == 0,
+                "workspace must be a 16-byte aligned device pointer");
+    const size_t need = b2a_fwd_workspace_bytes(a->batch, a->total_q, varlen ? 1 : 0);
+    if (a->workspace_bytes < need) {
+        return fail(B2A_ERR_WORKSPACE_TOO_SMALL, "workspace has %zu bytes, need %zu",
+                    a->workspace_bytes, need);
+    }
+
+    DeviceInfo dev{};
+    int rc = current_device_info(&dev);
+    if (rc != B2A_OK) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+
+    CUtensorMap map_q, map_k, map_v;
+    rc = make_token_map(&map_q, a->q, a->total_q, a->heads_q, kTileM);
+    if (rc != B2A_OK) return rc;
+    rc = make_token_map(&map_k, a->k, a->total_k, a->heads_k, kTileN);
+    if (rc != B2A_OK) return rc;
+    rc = make_token_map(&map_v, a->v, a->total_k, a->heads_k, kTileN);
+    if (rc != B2A_OK) return rc;
+
+    auto* hdr = static_cast<WorkspaceHeader*>(a->workspace);
+    int2* work_list = reinterpret_cast<int2*>(hdr + 1);
+    B2A_CUDA_OK(cudaMemsetAsync(hdr, 0, sizeof(WorkspaceHeader), stream));
+
+    FwdParams p{};
+    p.o = static_cast<__nv_bfloat16*>(a->out);
+    p.lse = a->lse;
+    p.cu_seqlens_q = a->cu_seqlens_q;
+    p.cu_seqlens_k = a->cu_seqlens_k;
+    p.work_list = varlen ? work_list : nullptr;
+    p.num_entries_dev = &hdr->num_entries;
+    p.sched_counter = &hdr->sched_counter;
+    p.status = &hdr->status;
+    p.batch = a->batch;
+    p.seqlen_q = a->seqlen_q;
+    p.seqlen_k = a->seqlen_k;
+    p.total_q = a->total_q;
+    p.total_k = a->total_k;
+    p.heads_q = a->heads_q;
+    p.heads_k = a->heads_k;
+    p.causal = a->is_causal ? 1 : 0;
+    p.scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / std::sqrt(static_cast<float>(kHeadDim));
+    p.scale_log2 = p.scale * kLog2e;
+    p.merge = a->merge_running ? 1 : 0;
+    p.timeout_ns = kDefaultTimeoutNs;
+
+    long long work_items;
+    if (varlen) {
+        const int cap = static_cast<int>(max_entries(a->batch, a->total_q, kFwdRowsPerWork));
+        rc = launch_varlen_plan(0, a->cu_seqlens_q, a->cu_seqlens_k, a->batch, p.causal, work_list,
+                                &hdr->num_entries, cap, stream);
+        if (rc != B2A_OK) return rc;
+        p.num_entries_host = cap;
+        p.lse_head_stride = a->total_q;
+        p.lse_batch_stride = 0;
+        work_items = static_cast<long long>(cap) * a->heads_q;
+    } else {
+        const int nmb = (a->seqlen_q + kFwdRowsPerWork - 1) / kFwdRowsPerWork;
+        p.num_entries_host = a->batch * nmb;
+        p.lse_head_stride = a->seqlen_q;
+        p.lse_batch_stride = static_cast<long long>(a->heads_q) * a->seqlen_q;
+        work_items = static_cast<long long>(p.num_entries_host) * a->heads_q;
+    }
+
+    int grid = a->grid_blocks > 0 ? a->grid_blocks : dev.sm_count;
+    if (work_items < grid) grid = static_cast<int>(work_items);
+    if (grid < 1) grid = 1;
+
+    if (p.merge) {
+        rc = configure_fwd_kernel<true>(dev);
+        if (rc != B2A_OK) return rc;
+        fwd_kernel<true><<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    } else {
+        rc = configure_fwd_kernel<false>(dev);
+        if (rc != B2A_OK) return rc;
+        fwd_kernel<false><<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    }
+    B2A_CUDA_OK(cudaGetLastError());
+    return B2A_OK;
+}
+
+}  // extern "C"

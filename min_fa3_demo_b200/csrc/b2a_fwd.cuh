@@ -1,0 +1,605 @@
+// Forward attention for sm_100a: O = softmax(scale * Q K^T [+ causal mask]) V, LSE.
+//
+// One persistent CTA per SM.  A work item is 256 query rows of one document and
+// one query head, processed as two 128-row tiles (A, B) that ping-pong on the
+// tensor core:
+//
+//   warp  0-3   softmax warpgroup of tile A (one thread per query row)
+//   warp  4-7   softmax warpgroup of tile B
+//   warp  8     tcgen05.mma issue
+//   warp  9     TMA loads and work fetch
+//   warp 10-11  idle (they only donate their registers)
+//
+// Tensor memory (512 columns): S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512).
+// P (bf16) overwrites the first 64 columns of its S tile and is consumed by the
+// P*V MMA straight from tensor memory.  K and V tiles travel through one shared
+// ring of 32 KiB stages in the order K(j0) V(j0) K(j0-1) V(j0-1) ...
+//
+// BSHD and varlen inputs share the code path: both are addressed as a flat
+// [tokens, heads, 128] tensor plus per-document (begin, length) pairs.
+#pragma once
+
+#include "b2a_ptx.cuh"
+
+namespace b2a {
+
+constexpr int kHeadDim = 128;
+constexpr int kTileM = 128;          // query rows per tile
+constexpr int kTileN = 128;          // key rows per K/V block
+constexpr int kFwdTilesPerCta = 2;   // tiles per work item
+constexpr int kFwdRowsPerWork = kTileM * kFwdTilesPerCta;
+constexpr int kFwdStages = 4;        // K/V ring stages
+constexpr int kFwdThreads = 384;
+constexpr uint32_t kTileBytes = kTileM * kHeadDim * 2;   // 32 KiB bf16 tile
+constexpr uint32_t kHalfTileBytes = kTileBytes / 2;      // one 64-column half
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units; lazy O rescale
+
+struct FwdParams {
+    __nv_bfloat16* o;            // [tokens_q, heads_q, 128]
+    float* lse;                  // see lse_head_stride / lse_batch_stride
+    const int* cu_seqlens_q;     // [batch + 1] or null for BSHD
+    const int* cu_seqlens_k;
+    const int2* work_list;       // varlen: (doc, m_block) in LPT order; null for BSHD
+    const int* num_entries_dev;  // varlen: number of work_list entries (device word)
+    int* sched_counter;          // zeroed before launch
+    unsigned int* status;
+    int batch;
+    int seqlen_q;                // BSHD: S_q.  varlen: unused
+    int seqlen_k;
+    int total_q;
+    int total_k;
+    int heads_q;
+    int heads_k;
+    int causal;
+    int num_entries_host;        // BSHD: batch * m_blocks.  varlen: upper bound (unused)
+    float scale;                 // softmax scale
+    float scale_log2;            // scale * log2(e)
+    long long lse_head_stride;   // elements between heads
+    long long lse_batch_stride;  // BSHD: elements between batches (heads_q * S_q)
+    // Running-merge mode (context-parallel steps): O/LSE already hold a partial
+    // result that this call's contribution is merged into.
+    int merge;
+    // Offset added to key positions for the causal rule: a key at local index c
+    // is visible to local query row r when c + k_pos_offset <= r + q_pos_offset + (k_len - q_len)
+    // (both 0 for plain attention).
+    uint32_t timeout_ns;
+};
+
+struct FwdWork {
+    int q_begin;   // first token of the document in the flat Q tensor
+    int q_len;
+    int k_begin;
+    int k_len;
+    int m0;        // first query row (document-local) of the work item
+    int head;
+    int head_k;
+    long long lse_base;   // element offset of document row 0 for this head
+};
+
+struct __align__(1024) FwdShared {
+    uint8_t q[kFwdTilesPerCta][kTileBytes];
+    uint8_t kv[kFwdStages][kTileBytes];
+    uint64_t q_full[kFwdTilesPerCta];
+    uint64_t q_empty[kFwdTilesPerCta];
+    uint64_t kv_full[kFwdStages];
+    uint64_t kv_empty[kFwdStages];
+    uint64_t s_full[kFwdTilesPerCta];
+    uint64_t p_full[kFwdTilesPerCta];
+    uint64_t o_full[kFwdTilesPerCta];
+    uint64_t sched_full[2];
+    uint64_t sched_empty[2];
+    int sched_w[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+__device__ __forceinline__ FwdWork fwd_decode_work(const FwdParams& p, int w) {
+    FwdWork wk;
+    int entry = w / p.heads_q;
+    wk.head = w - entry * p.heads_q;
+    wk.head_k = wk.head / (p.heads_q / p.heads_k);
+    if (p.cu_seqlens_q == nullptr) {
+        int nmb = (p.seqlen_q + kFwdRowsPerWork - 1) / kFwdRowsPerWork;
+        int b = entry / nmb;
+        int mi = entry - b * nmb;
+        int mblk = p.causal ? (nmb - 1 - mi) : mi;
+        wk.q_begin = b * p.seqlen_q;
+        wk.q_len = p.seqlen_q;
+        wk.k_begin = b * p.seqlen_k;
+        wk.k_len = p.seqlen_k;
+        wk.m0 = mblk * kFwdRowsPerWork;
+        wk.lse_base = static_cast<long long>(b) * p.lse_batch_stride +
+                      static_cast<long long>(wk.head) * p.lse_head_stride;
+    } else {
+        int2 e = p.work_list[entry];
+        int doc = e.x;
+        wk.q_begin = p.cu_seqlens_q[doc];
+        wk.q_len = p.cu_seqlens_q[doc + 1] - wk.q_begin;
+        wk.k_begin = p.cu_seqlens_k[doc];
+        wk.k_len = p.cu_seqlens_k[doc + 1] - wk.k_begin;
+        wk.m0 = e.y * kFwdRowsPerWork;
+        wk.lse_base = static_cast<long long>(wk.head) * p.lse_head_stride + wk.q_begin;
+    }
+    return wk;
+}
+
+// Number of K/V blocks tile `x` of the work item needs (0 when the tile has no
+// query row, or no visible key).
+__device__ __forceinline__ int fwd_num_kv_blocks(const FwdParams& p, const FwdWork& wk, int x) {
+    int row0 = wk.m0 + x * kTileM;
+    if (row0 >= wk.q_len) {
+        return 0;
+    }
+    int limit = wk.k_len;
+    if (p.causal) {
+        int row_last = min(row0 + kTileM, wk.q_len) - 1;
+        limit = min(limit, row_last + 1 + wk.k_len - wk.q_len);
+    }
+    if (limit <= 0) {
+        return 0;
+    }
+    return (limit + kTileN - 1) / kTileN;
+}
+
+template <bool kMerge>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+           const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    FwdShared& sh = *reinterpret_cast<FwdShared*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kFwdTilesPerCta; ++i) {
+            mbar_init(smem_u32(&sh.q_full[i]), 1);
+            mbar_init(smem_u32(&sh.q_empty[i]), 1);
+            mbar_init(smem_u32(&sh.s_full[i]), 1);
+            mbar_init(smem_u32(&sh.p_full[i]), kTileM);
+            mbar_init(smem_u32(&sh.o_full[i]), 1);
+        }
+        for (int i = 0; i < kFwdStages; ++i) {
+            mbar_init(smem_u32(&sh.kv_full[i]), 1);
+            mbar_init(smem_u32(&sh.kv_empty[i]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&sh.sched_full[i]), 1);
+            mbar_init(smem_u32(&sh.sched_empty[i]), 1 + 2 * 4);  // MMA warp + 8 softmax warps
+        }
+        sh.abort_flag = 0;
+        fence_mbar_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 8) {
+        tmem_alloc(smem_u32(&sh.tmem_base), 512);
+        tmem_relinquish();
+        tc_fence_before_sync();
+    }
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&sh.tmem_base);
+
+    WaitCtx wctx{smem_u32(&sh.abort_flag), p.status, p.timeout_ns};
+
+    const int total_work =
+        (p.cu_seqlens_q == nullptr ? p.num_entries_host : *p.num_entries_dev) * p.heads_q;
+
+    if (warp >= 8) {
+        reg_dealloc<72>();
+        if (warp == 9) {
+            // ------------------------------------------------------------ load warp
+            if (lane == 0) {
+                tma_prefetch_desc(&map_q);
+                tma_prefetch_desc(&map_k);
+                tma_prefetch_desc(&map_v);
+            }
+            uint32_t kv_it = 0;
+            uint32_t q_cnt[2] = {0, 0};
+            bool ok = true;
+            for (uint32_t it = 0; ok; ++it) {
+                const uint32_t slot = it & 1u;
+                ok = mbar_wait(wctx, smem_u32(&sh.sched_empty[slot]), ((it >> 1) & 1u) ^ 1u, 1);
+                if (!ok) break;
+                int w = 0;
+                if (lane == 0) {
+                    w = atomicAdd(p.sched_counter, 1);
+                    if (w >= total_work) w = -1;
+                    sh.sched_w[slot] = w;
+                }
+                w = __shfl_sync(0xFFFFFFFFu, w, 0);
+                if (lane == 0) {
+                    mbar_arrive(smem_u32(&sh.sched_full[slot]));
+                }
+                if (w < 0) break;
+                const FwdWork wk = fwd_decode_work(p, w);
+                int nblk[2] = {fwd_num_kv_blocks(p, wk, 0), fwd_num_kv_blocks(p, wk, 1)};
+                const int n_max = max(nblk[0], nblk[1]);
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    if (nblk[x] > 0) {
+                        ok = mbar_wait(wctx, smem_u32(&sh.q_empty[x]), (q_cnt[x] & 1u) ^ 1u, 2);
+                        if (!ok) break;
+                        ++q_cnt[x];
+                        if (lane == 0) {
+                            const uint32_t bar = smem_u32(&sh.q_full[x]);
+                            const uint32_t dst = smem_u32(&sh.q[x][0]);
+                            const int row = wk.q_begin + wk.m0 + x * kTileM;
+                            mbar_arrive_expect_tx(bar, kTileBytes);
+                            tma_load_3d(dst, &map_q, bar, 0, wk.head, row);
+                            tma_load_3d(dst + kHalfTileBytes, &map_q, bar, 64, wk.head, row);
+                        }
+                    }
+                }
+                for (int j = n_max - 1; j >= 0 && ok; --j) {
+#pragma unroll
+                    for (int kv = 0; kv < 2; ++kv) {
+                        const uint32_t stage = kv_it % kFwdStages;
+                        ok = mbar_wait(wctx, smem_u32(&sh.kv_empty[stage]),
+                                       ((kv_it / kFwdStages) & 1u) ^ 1u, 3);
+                        if (!ok) break;
+                        ++kv_it;
+                        if (lane == 0) {
+                            const uint32_t bar = smem_u32(&sh.kv_full[stage]);
+                            const uint32_t dst = smem_u32(&sh.kv[stage][0]);
+                            const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
+                            const int row = wk.k_begin + j * kTileN;
+                            mbar_arrive_expect_tx(bar, kTileBytes);
+                            tma_load_3d(dst, map, bar, 0, wk.head_k, row);
+                            tma_load_3d(dst + kHalfTileBytes, map, bar, 64, wk.head_k, row);
+                        }
+                    }
+                }
+            }
+        } else if (warp == 8) {
+            // ------------------------------------------------------------ MMA warp
+            constexpr uint32_t idesc_qk = make_idesc_bf16(kTileM, kTileN, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_bf16(kTileM, kHeadDim, 0, 1);
+            uint32_t kv_it = 0;
+            uint32_t q_cnt[2] = {0, 0};
+            uint32_t p_cnt[2] = {0, 0};
+            bool ok = true;
+            const uint32_t s_tmem[2] = {tmem_base + 0u, tmem_base + 128u};
+            const uint32_t o_tmem[2] = {tmem_base + 256u, tmem_base + 384u};
+
+            // S_x = Q_x * K^T for the K tile in `stage` (8 k-steps of 16 over head_dim).
+            auto issue_qk = [&](int x, uint32_t stage) {
+                const uint32_t q_addr = smem_u32(&sh.q[x][0]);
+                const uint32_t k_addr = smem_u32(&sh.kv[stage][0]);
+#pragma unroll
+                for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
+                    const uint64_t a = make_smem_desc_sw128(q_addr + off, 16, 1024);
+                    const uint64_t b = make_smem_desc_sw128(k_addr + off, 16, 1024);
+                    umma_ss(s_tmem[x], a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+            };
+            // O_x (+)= P_x * V for the V tile in `stage` (8 k-steps of 16 over keys).
+            auto issue_pv = [&](int x, uint32_t stage, uint32_t accumulate) {
+                const uint32_t v_addr = smem_u32(&sh.kv[stage][0]);
+#pragma unroll
+                for (int ks = 0; ks < kTileN / 16; ++ks) {
+                    const uint64_t b =
+                        make_smem_desc_sw128(v_addr + ks * 2048, kHalfTileBytes, 1024);
+                    umma_ts(o_tmem[x], s_tmem[x] + ks * 8, b, idesc_pv,
+                            (ks > 0 || accumulate) ? 1u : 0u);
+                }
+            };
+
+            for (uint32_t it = 0; ok; ++it) {
+                const uint32_t slot = it & 1u;
+                ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 4);
+                if (!ok) break;
+                const int w = *reinterpret_cast<volatile int*>(&sh.sched_w[slot]);
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(smem_u32(&sh.sched_empty[slot]));
+                }
+                if (w < 0) break;
+                const FwdWork wk = fwd_decode_work(p, w);
+                int nblk[2] = {fwd_num_kv_blocks(p, wk, 0), fwd_num_kv_blocks(p, wk, 1)};
+                const int n_max = max(nblk[0], nblk[1]);
+                if (n_max == 0) continue;
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    if (nblk[x] > 0) {
+                        ok = ok && mbar_wait(wctx, smem_u32(&sh.q_full[x]), q_cnt[x] & 1u, 5);
+                        ++q_cnt[x];
+                    }
+                }
+                if (!ok) break;
+                // Prologue: S(j0) for every tile that owns block j0.
+                {
+                    const int j0 = n_max - 1;
+                    const uint32_t stage = kv_it % kFwdStages;
+                    ok = mbar_wait(wctx, smem_u32(&sh.kv_full[stage]), (kv_it / kFwdStages) & 1u, 6);
+                    if (!ok) break;
+                    ++kv_it;
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int x = 0; x < 2; ++x) {
+                            if (j0 < nblk[x]) {
+                                issue_qk(x, stage);
+                                tc_commit(smem_u32(&sh.s_full[x]));
+                                if (j0 == 0) tc_commit(smem_u32(&sh.q_empty[x]));
+                            }
+                        }
+                        tc_commit(smem_u32(&sh.kv_empty[stage]));
+                    }
+                    __syncwarp();
+                }
+                for (int j = n_max - 1; j >= 0 && ok; --j) {
+                    const uint32_t stage_v = kv_it % kFwdStages;
+                    ok = mbar_wait(wctx, smem_u32(&sh.kv_full[stage_v]),
+                                   (kv_it / kFwdStages) & 1u, 7);
+                    if (!ok) break;
+                    ++kv_it;
+                    uint32_t stage_k = 0;
+                    if (j > 0) {
+                        stage_k = kv_it % kFwdStages;
+                    }
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        if (j < nblk[x]) {
+                            ok = mbar_wait(wctx, smem_u32(&sh.p_full[x]), p_cnt[x] & 1u, 8);
+                            if (!ok) break;
+                            ++p_cnt[x];
+                            tc_fence_after_sync();
+                            if (lane == 0) {
+                                issue_pv(x, stage_v, j != nblk[x] - 1 ? 1u : 0u);
+                                if (j == 0) tc_commit(smem_u32(&sh.o_full[x]));
+                            }
+                            __syncwarp();
+                        }
+                        if (x == 1 && lane == 0) {
+                            tc_commit(smem_u32(&sh.kv_empty[stage_v]));
+                        }
+                        if (j > 0) {
+                            if (x == 0) {
+                                ok = mbar_wait(wctx, smem_u32(&sh.kv_full[stage_k]),
+                                               (kv_it / kFwdStages) & 1u, 9);
+                                if (!ok) break;
+                                tc_fence_after_sync();
+                            }
+                            if (j - 1 < nblk[x] && lane == 0) {
+                                issue_qk(x, stage_k);
+                                tc_commit(smem_u32(&sh.s_full[x]));
+                                if (j - 1 == 0) tc_commit(smem_u32(&sh.q_empty[x]));
+                            }
+                            if (x == 1 && lane == 0) {
+                                tc_commit(smem_u32(&sh.kv_empty[stage_k]));
+                            }
+                            __syncwarp();
+                        }
+                    }
+                    if (j > 0) ++kv_it;
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax warpgroups
+        reg_alloc<216>();
+        const int x = warp >> 2;                        // tile index
+        const int r = (warp & 3) * 32 + lane;           // row within the tile
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t s_tmem = tmem_base + lane_base + static_cast<uint32_t>(x) * 128u;
+        const uint32_t o_tmem = tmem_base + lane_base + 256u + static_cast<uint32_t>(x) * 128u;
+        uint32_t s_cnt = 0;
+        uint32_t o_cnt = 0;
+        bool ok = true;
+        const float sl2 = p.scale_log2;
+
+        for (uint32_t it = 0; ok; ++it) {
+            const uint32_t slot = it & 1u;
+            ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 10);
+            if (!ok) break;
+            const int w = *reinterpret_cast<volatile int*>(&sh.sched_w[slot]);
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&sh.sched_empty[slot]));
+            }
+            if (w < 0) break;
+            const FwdWork wk = fwd_decode_work(p, w);
+            const int tile_row0 = wk.m0 + x * kTileM;
+            if (tile_row0 >= wk.q_len) continue;
+            const int nblk = fwd_num_kv_blocks(p, wk, x);
+            const int row = tile_row0 + r;
+            const bool row_valid = row < wk.q_len;
+            const long long tok = static_cast<long long>(wk.q_begin) + row;
+            __nv_bfloat16* o_row = p.o + (tok * p.heads_q + wk.head) * kHeadDim;
+            float* lse_ptr = p.lse + wk.lse_base + row;
+
+            // Key columns [0, col_limit) are visible to this row.
+            int col_limit = wk.k_len;
+            if (p.causal) {
+                col_limit = min(col_limit, row + 1 + wk.k_len - wk.q_len);
+            }
+            // Smallest limit in the tile (its first row) decides whether a block needs masking.
+            int tile_min_limit = wk.k_len;
+            if (p.causal) {
+                tile_min_limit = min(tile_min_limit, tile_row0 + 1 + wk.k_len - wk.q_len);
+            }
+
+            float m_used = -INFINITY;   // running reference max (raw score units)
+            float l = 0.f;              // running row sum relative to m_used
+
+            for (int j = nblk - 1; j >= 0; --j) {
+                ok = mbar_wait(wctx, smem_u32(&sh.s_full[x]), s_cnt & 1u, 11);
+                if (!ok) break;
+                ++s_cnt;
+                tc_fence_after_sync();
+
+                float s[kTileN];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t t[32];
+                    tmem_ld_x32(s_tmem + c * 32, t);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(t[i]);
+                }
+                tmem_wait_ld();
+
+                const int n0 = j * kTileN;
+                if (n0 + kTileN > tile_min_limit) {
+                    const int lim = col_limit - n0;
+#pragma unroll
+                    for (int i = 0; i < kTileN; ++i) {
+                        if (i >= lim) s[i] = -INFINITY;
+                    }
+                }
+
+                float bm = s[0];
+#pragma unroll
+                for (int i = 1; i < kTileN; ++i) bm = fmaxf(bm, s[i]);
+
+                const bool first = (j == nblk - 1);
+                const float m_new = fmaxf(m_used, bm);
+                if (first) {
+                    m_used = m_new;
+                } else {
+                    const bool want = (m_new - m_used) * sl2 > kRescaleThreshold;
+                    if (__any_sync(0xFFFFFFFFu, want)) {
+                        const float factor =
+                            (m_new == -INFINITY) ? 1.f : fast_exp2((m_used - m_new) * sl2);
+                        l *= factor;
+                        m_used = m_new;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t t[32];
+                            tmem_ld_x32(o_tmem + c * 32, t);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                t[i] = __float_as_uint(__uint_as_float(t[i]) * factor);
+                            }
+                            tmem_st_x32(o_tmem + c * 32, t);
+                        }
+                    }
+                }
+
+                const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used * sl2;
+                float sum = 0.f;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t t[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float p0 = fast_exp2(fmaf(s[c * 64 + 2 * i], sl2, neg_m));
+                        const float p1 = fast_exp2(fmaf(s[c * 64 + 2 * i + 1], sl2, neg_m));
+                        sum += p0 + p1;
+                        t[i] = pack_bf16x2(p0, p1);
+                    }
+                    tmem_st_x32(s_tmem + c * 32, t);
+                }
+                l += sum;
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&sh.p_full[x]));
+            }
+            if (!ok) break;
+
+            float inv = 0.f;
+            float lse_val = -INFINITY;
+            if (nblk > 0) {
+                ok = mbar_wait(wctx, smem_u32(&sh.o_full[x]), o_cnt & 1u, 12);
+                if (!ok) break;
+                ++o_cnt;
+                tc_fence_after_sync();
+                if (l > 0.f) {
+                    inv = 1.f / l;
+                    lse_val = (m_used * sl2 + fast_log2(l)) * kLn2;
+                }
+            }
+
+            if constexpr (kMerge) {
+                // Merge this call's (O_b, L_b) into the running (O_p, L_p):
+                //   L = logaddexp(L_p, L_b);  O = O_p * e^(L_p - L) + O_b * e^(L_b - L)
+                float lse_prev = row_valid ? *lse_ptr : -INFINITY;
+                float lse_new = lse_prev;
+                float w_prev = 1.f;
+                float w_blk = 0.f;
+                if (lse_val != -INFINITY) {
+                    const float mx = fmaxf(lse_prev, lse_val);
+                    const float e_prev = (lse_prev == -INFINITY) ? 0.f : __expf(lse_prev - mx);
+                    const float e_blk = __expf(lse_val - mx);
+                    const float den = e_prev + e_blk;
+                    lse_new = mx + __logf(den);
+                    w_prev = e_prev / den;
+                    w_blk = e_blk / den;
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t t[32];
+                    if (nblk > 0) {
+                        tmem_ld_x32(o_tmem + c * 32, t);
+                        tmem_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) t[i] = 0u;
+                    }
+                    if (row_valid) {
+                        uint4* dst = reinterpret_cast<uint4*>(o_row + c * 32);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 prev = dst[v];
+                            uint32_t pw[4] = {prev.x, prev.y, prev.z, prev.w};
+                            uint32_t out[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float a0 = __uint_as_float(pw[e] << 16);
+                                const float a1 = __uint_as_float(pw[e] & 0xFFFF0000u);
+                                const float b0 = __uint_as_float(t[v * 8 + 2 * e]) * inv;
+                                const float b1 = __uint_as_float(t[v * 8 + 2 * e + 1]) * inv;
+                                out[e] = pack_bf16x2(a0 * w_prev + b0 * w_blk,
+                                                     a1 * w_prev + b1 * w_blk);
+                            }
+                            dst[v] = make_uint4(out[0], out[1], out[2], out[3]);
+                        }
+                    }
+                }
+                if (row_valid) *lse_ptr = lse_new;
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t t[32];
+                    if (nblk > 0) {
+                        tmem_ld_x32(o_tmem + c * 32, t);
+                        tmem_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) t[i] = 0u;
+                    }
+                    if (row_valid) {
+                        uint4* dst = reinterpret_cast<uint4*>(o_row + c * 32);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint32_t out[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                out[e] = pack_bf16x2(__uint_as_float(t[v * 8 + 2 * e]) * inv,
+                                                     __uint_as_float(t[v * 8 + 2 * e + 1]) * inv);
+                            }
+                            dst[v] = make_uint4(out[0], out[1], out[2], out[3]);
+                        }
+                    }
+                }
+                if (row_valid) *lse_ptr = lse_val;
+            }
+            tc_fence_before_sync();
+        }
+    }
+
+    // Common exit: every role arrives here (normally or after an abort).
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace b2a
