@@ -1,0 +1,828 @@
+// Backward attention for sm_100a.
+//
+// Three kernels on one stream:
+//   bwd_preprocess_kernel  D = rowsum(dO * O), LSE2 = LSE * log2(e) (padded per document)
+//   bwd_kernel             dK, dV (bf16, written directly) and fp32 dQ partial sums
+//   bwd_postprocess_kernel dQ = bf16(scale * dq_accum)
+//
+// bwd_kernel keeps one 128-row K/V block of one KV head stationary per work item and
+// loops over every (query head of the group, 128-row query tile) that sees it, so dK and
+// dV accumulate in tensor memory across the whole loop (GQA included) and need no fp32
+// global accumulators.  Everything is computed transposed (FA-style "S^T = K Q^T"): a
+// compute thread owns one key row, P^T goes back to tensor memory as the A operand of
+// dV += P^T dO, and dS^T is written once to shared memory where it is both the K-major A
+// operand of dK += dS^T Q and the MN-major A operand of dQ = dS K.
+//
+//   warp  0-3   compute warpgroup 0: query columns 0-63 of the S^T / dP^T tiles
+//   warp  4-7   compute warpgroup 1: query columns 64-127
+//   warp  8-11  dQ warpgroup: drains dQ tiles from tensor memory, red.add into dq_accum
+//   warp 12     tcgen05.mma issue
+//   warp 13     TMA loads and work fetch
+//   warp 14-15  idle
+//
+// Tensor memory (512 columns): S^T/P^T [0,128)  dP^T/dQ [128,256)  dV [256,384)  dK [384,512).
+#pragma once
+
+#include "b2a_fwd.cuh"
+
+namespace b2a {
+
+constexpr int kBwdThreads = 512;
+constexpr int kBwdStages = 2;          // Q / dO ring stages
+constexpr uint32_t kRowVecBytes = kTileM * 4;   // 128 fp32 (LSE2 or D of one query tile)
+
+// dq_accum layout: [head][padded 128-row tile][32 column chunks][128 rows][4 floats], so a
+// warp-wide 16-byte red.add touches 512 contiguous bytes.
+constexpr int kDqTileFloats = kTileM * kHeadDim;
+
+struct BwdParams {
+    __nv_bfloat16* dk;             // [tokens_k, heads_k, 128]
+    __nv_bfloat16* dv;
+    float* dq_accum;               // see layout above
+    const float* lse2;             // [heads_q, padded_q]  (LSE * log2 e; +inf = row contributes nothing)
+    const float* dpsum;            // [heads_q, padded_q]  rowsum(dO * O)
+    const int* cu_seqlens_q;
+    const int* cu_seqlens_k;
+    const int2* work_list;         // varlen: (doc, n_block) in LPT order
+    const int* num_entries_dev;
+    int* sched_counter;
+    unsigned int* status;
+    int batch;
+    int seqlen_q;
+    int seqlen_k;
+    int heads_q;
+    int heads_k;
+    int causal;
+    int num_entries_host;
+    int padded_q;                  // padded query rows per head (multiple of 128)
+    float scale;
+    float scale_log2;
+    uint32_t timeout_ns;
+};
+
+struct BwdWork {
+    int q_begin;
+    int q_len;
+    int k_begin;
+    int k_len;
+    int q_pad_begin;   // first padded row of the document (multiple of 128)
+    int n0;            // first key row (document-local) of the block
+    int head_k;
+    int m_first;       // first query tile that sees the block
+    int m_count;       // number of query tiles
+};
+
+// Padded row offset of a document: every document starts on a 128-row boundary and owns
+// at least round_up(len, 128) rows.
+__host__ __device__ __forceinline__ int bwd_padded_begin(int cu_begin, int doc) {
+    return ((cu_begin + 127) / 128) * 128 + 256 * doc;
+}
+
+__device__ __forceinline__ BwdWork bwd_decode_work(const BwdParams& p, int w) {
+    BwdWork wk;
+    int entry = w / p.heads_k;
+    wk.head_k = w - entry * p.heads_k;
+    int nblk;
+    if (p.cu_seqlens_q == nullptr) {
+        int nnb = (p.seqlen_k + kTileN - 1) / kTileN;
+        int b = entry / nnb;
+        int ni = entry - b * nnb;
+        // Causal: early key blocks are seen by the most query tiles -> run them first.
+        nblk = ni;
+        wk.q_begin = b * p.seqlen_q;
+        wk.q_len = p.seqlen_q;
+        wk.k_begin = b * p.seqlen_k;
+        wk.k_len = p.seqlen_k;
+        wk.q_pad_begin = b * (((p.seqlen_q + 127) / 128) * 128);
+    } else {
+        int2 e = p.work_list[entry];
+        int doc = e.x;
+        nblk = e.y;
+        wk.q_begin = p.cu_seqlens_q[doc];
+        wk.q_len = p.cu_seqlens_q[doc + 1] - wk.q_begin;
+        wk.k_begin = p.cu_seqlens_k[doc];
+        wk.k_len = p.cu_seqlens_k[doc + 1] - wk.k_begin;
+        wk.q_pad_begin = bwd_padded_begin(wk.q_begin, doc);
+    }
+    wk.n0 = nblk * kTileN;
+    int m_tiles = (wk.q_len + kTileM - 1) / kTileM;
+    int first = 0;
+    if (p.causal) {
+        int first_row = max(0, wk.n0 + wk.q_len - wk.k_len);
+        first = min(m_tiles, first_row / kTileM);
+    }
+    wk.m_first = first;
+    wk.m_count = m_tiles - first;
+    return wk;
+}
+
+struct __align__(1024) BwdShared {
+    uint8_t k[kTileBytes];
+    uint8_t v[kTileBytes];
+    uint8_t q[kBwdStages][kTileBytes];
+    uint8_t dout[kBwdStages][kTileBytes];
+    uint8_t ds[kTileBytes];
+    float lse2[kBwdStages][kTileM];
+    float dpsum[kBwdStages][kTileM];
+    uint64_t kv_full;
+    uint64_t kv_empty;
+    uint64_t q_full[kBwdStages];
+    uint64_t q_empty[kBwdStages];
+    uint64_t do_full[kBwdStages];
+    uint64_t do_empty[kBwdStages];
+    uint64_t s_full;
+    uint64_t dp_full;
+    uint64_t p_ready;
+    uint64_t ds_ready;
+    uint64_t ds_empty;
+    uint64_t dq_full;
+    uint64_t dq_drained;
+    uint64_t dkv_full;
+    uint64_t dkv_empty;
+    uint64_t sched_full[2];
+    uint64_t sched_empty[2];
+    int sched_w[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+           const BwdParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    BwdShared& sh = *reinterpret_cast<BwdShared*>(smem_raw);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if ((smem_u32(smem_raw) & 1023u) != 0u) {
+        // The swizzled tiles need a 1 KiB aligned base; report instead of computing garbage.
+        if (threadIdx.x == 0) set_status(p.status, kStatusBadArg, 1);
+        return;
+    }
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&sh.kv_full), 1);
+        mbar_init(smem_u32(&sh.kv_empty), 1);
+        for (int i = 0; i < kBwdStages; ++i) {
+            mbar_init(smem_u32(&sh.q_full[i]), 1);
+            mbar_init(smem_u32(&sh.q_empty[i]), 1);
+            mbar_init(smem_u32(&sh.do_full[i]), 1);
+            mbar_init(smem_u32(&sh.do_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&sh.s_full), 1);
+        mbar_init(smem_u32(&sh.dp_full), 1);
+        mbar_init(smem_u32(&sh.p_ready), 256);
+        mbar_init(smem_u32(&sh.ds_ready), 256);
+        mbar_init(smem_u32(&sh.ds_empty), 1);
+        mbar_init(smem_u32(&sh.dq_full), 1);
+        mbar_init(smem_u32(&sh.dq_drained), 128);
+        mbar_init(smem_u32(&sh.dkv_full), 1);
+        mbar_init(smem_u32(&sh.dkv_empty), 256);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&sh.sched_full[i]), 1);
+            mbar_init(smem_u32(&sh.sched_empty[i]), 1 + 12);   // MMA warp + 12 consumer warps
+        }
+        sh.abort_flag = 0;
+        fence_mbar_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 12) {
+        tmem_alloc(smem_u32(&sh.tmem_base), 512);
+        tmem_relinquish();
+        tc_fence_before_sync();
+    }
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&sh.tmem_base);
+    constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
+
+    WaitCtx wctx{smem_u32(&sh.abort_flag), p.status, p.timeout_ns};
+    const int total_work =
+        (p.cu_seqlens_q == nullptr ? p.num_entries_host : *p.num_entries_dev) * p.heads_k;
+    const int group = p.heads_q / p.heads_k;
+
+    if (warp >= 12) {
+        reg_dealloc<88>();
+        if (warp == 13) {
+            // ------------------------------------------------------------ load warp
+            if (lane == 0) {
+                tma_prefetch_desc(&map_q);
+                tma_prefetch_desc(&map_k);
+                tma_prefetch_desc(&map_v);
+                tma_prefetch_desc(&map_do);
+            }
+            uint32_t item_cnt = 0;   // work items that loaded K/V
+            uint32_t step_it = 0;    // global (h, m) step counter -> Q/dO ring position
+            bool ok = true;
+            for (uint32_t it = 0; ok; ++it) {
+                const uint32_t slot = it & 1u;
+                ok = mbar_wait(wctx, smem_u32(&sh.sched_empty[slot]), ((it >> 1) & 1u) ^ 1u, 1);
+                if (!ok) break;
+                int w = 0;
+                if (lane == 0) {
+                    w = atomicAdd(p.sched_counter, 1);
+                    if (w >= total_work) w = -1;
+                    sh.sched_w[slot] = w;
+                }
+                w = __shfl_sync(0xFFFFFFFFu, w, 0);
+                if (lane == 0) mbar_arrive(smem_u32(&sh.sched_full[slot]));
+                if (w < 0) break;
+                const BwdWork wk = bwd_decode_work(p, w);
+                const int steps = wk.m_count * group;
+                if (steps == 0) continue;
+                ok = mbar_wait(wctx, smem_u32(&sh.kv_empty), (item_cnt & 1u) ^ 1u, 2);
+                if (!ok) break;
+                ++item_cnt;
+                if (lane == 0) {
+                    const uint32_t bar = smem_u32(&sh.kv_full);
+                    const int row = wk.k_begin + wk.n0;
+                    mbar_arrive_expect_tx(bar, 2 * kTileBytes);
+                    tma_load_3d(smem_u32(&sh.k[0]), &map_k, bar, 0, wk.head_k, row);
+                    tma_load_3d(smem_u32(&sh.k[0]) + kHalfTileBytes, &map_k, bar, 64, wk.head_k, row);
+                    tma_load_3d(smem_u32(&sh.v[0]), &map_v, bar, 0, wk.head_k, row);
+                    tma_load_3d(smem_u32(&sh.v[0]) + kHalfTileBytes, &map_v, bar, 64, wk.head_k, row);
+                }
+                for (int t = 0; t < steps && ok; ++t) {
+                    const int hq = wk.head_k * group + t / wk.m_count;
+                    const int m = wk.m_first + t % wk.m_count;
+                    const uint32_t stage = step_it % kBwdStages;
+                    const uint32_t par = ((step_it / kBwdStages) & 1u) ^ 1u;
+                    ++step_it;
+                    ok = mbar_wait(wctx, smem_u32(&sh.q_empty[stage]), par, 3);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t bar = smem_u32(&sh.q_full[stage]);
+                        const uint32_t dst = smem_u32(&sh.q[stage][0]);
+                        const int row = wk.q_begin + m * kTileM;
+                        const long long vec =
+                            static_cast<long long>(hq) * p.padded_q + wk.q_pad_begin + m * kTileM;
+                        mbar_arrive_expect_tx(bar, kTileBytes + 2 * kRowVecBytes);
+                        tma_load_3d(dst, &map_q, bar, 0, hq, row);
+                        tma_load_3d(dst + kHalfTileBytes, &map_q, bar, 64, hq, row);
+                        bulk_load_1d(smem_u32(&sh.lse2[stage][0]), p.lse2 + vec, kRowVecBytes, bar);
+                        bulk_load_1d(smem_u32(&sh.dpsum[stage][0]), p.dpsum + vec, kRowVecBytes, bar);
+                    }
+                    ok = mbar_wait(wctx, smem_u32(&sh.do_empty[stage]), par, 4);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t bar = smem_u32(&sh.do_full[stage]);
+                        const uint32_t dst = smem_u32(&sh.dout[stage][0]);
+                        const int row = wk.q_begin + m * kTileM;
+                        mbar_arrive_expect_tx(bar, kTileBytes);
+                        tma_load_3d(dst, &map_do, bar, 0, hq, row);
+                        tma_load_3d(dst + kHalfTileBytes, &map_do, bar, 64, hq, row);
+                    }
+                }
+            }
+        } else if (warp == 12) {
+            // ------------------------------------------------------------ MMA warp
+            constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);   // K-major A, K-major B
+            constexpr uint32_t idesc_kn = make_idesc_bf16(128, 128, 0, 1);   // K-major A, MN-major B
+            constexpr uint32_t idesc_nn = make_idesc_bf16(128, 128, 1, 1);   // MN-major A, MN-major B
+            const uint32_t k_addr = smem_u32(&sh.k[0]);
+            const uint32_t v_addr = smem_u32(&sh.v[0]);
+            const uint32_t ds_addr = smem_u32(&sh.ds[0]);
+
+            // D[128 x 128] = A * B^T with both operands K-major [rows][128] tiles.
+            auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
+                    umma_ss(d_tmem, make_smem_desc_sw128(a_addr + off, 16, 1024),
+                            make_smem_desc_sw128(b_addr + off, 16, 1024), idesc_kk,
+                            ks > 0 ? 1u : 0u);
+                }
+            };
+
+            uint32_t item_cnt = 0;
+            uint32_t step_it = 0;
+            uint32_t p_cnt = 0, ds_cnt = 0, drain_cnt = 0;
+            bool ok = true;
+            for (uint32_t it = 0; ok; ++it) {
+                const uint32_t slot = it & 1u;
+                ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 5);
+                if (!ok) break;
+                const int w = *reinterpret_cast<volatile int*>(&sh.sched_w[slot]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sh.sched_empty[slot]));
+                if (w < 0) break;
+                const BwdWork wk = bwd_decode_work(p, w);
+                const int steps = wk.m_count * group;
+                if (steps == 0) continue;
+                ok = mbar_wait(wctx, smem_u32(&sh.kv_full), item_cnt & 1u, 6);
+                if (!ok) break;
+                const uint32_t dkv_parity = (item_cnt & 1u) ^ 1u;
+                ++item_cnt;
+
+                // Prologue: S^T(0) and dP^T(0).
+                {
+                    const uint32_t stage = step_it % kBwdStages;
+                    const uint32_t par = (step_it / kBwdStages) & 1u;
+                    ok = mbar_wait(wctx, smem_u32(&sh.q_full[stage]), par, 8);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+                        issue_kmajor(tmem_base + kColS, k_addr, smem_u32(&sh.q[stage][0]));
+                        tc_commit(smem_u32(&sh.s_full));
+                    }
+                    __syncwarp();
+                    ok = mbar_wait(wctx, smem_u32(&sh.do_full[stage]), par, 9);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+                        issue_kmajor(tmem_base + kColDP, v_addr, smem_u32(&sh.dout[stage][0]));
+                        tc_commit(smem_u32(&sh.dp_full));
+                    }
+                    __syncwarp();
+                }
+                for (int t = 0; t < steps && ok; ++t) {
+                    const uint32_t stage = step_it % kBwdStages;
+                    const uint32_t nstage = (step_it + 1) % kBwdStages;
+                    const uint32_t npar = ((step_it + 1) / kBwdStages) & 1u;
+                    ++step_it;
+                    const uint32_t q_addr = smem_u32(&sh.q[stage][0]);
+                    const uint32_t do_addr = smem_u32(&sh.dout[stage][0]);
+                    const bool has_next = t + 1 < steps;
+
+                    // dV += P^T dO   (A = P^T from tensor memory, B = dO as MN-major)
+                    ok = mbar_wait(wctx, smem_u32(&sh.p_ready), p_cnt & 1u, 10);
+                    if (!ok) break;
+                    ++p_cnt;
+                    if (t == 0) {
+                        // dK/dV accumulators must have been read out by the previous item's
+                        // epilogue before they are overwritten.
+                        ok = mbar_wait(wctx, smem_u32(&sh.dkv_empty), dkv_parity, 7);
+                        if (!ok) break;
+                    }
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) {
+                            const uint32_t a_col = kColS + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
+                            umma_ts(tmem_base + kColDV, tmem_base + a_col,
+                                    make_smem_desc_sw128(do_addr + ks * 2048, kHalfTileBytes, 1024),
+                                    idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
+                        }
+                        tc_commit(smem_u32(&sh.do_empty[stage]));
+                    }
+                    __syncwarp();
+                    // S^T(t+1) = K Q(t+1)^T
+                    if (has_next) {
+                        ok = mbar_wait(wctx, smem_u32(&sh.q_full[nstage]), npar, 11);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        if (lane == 0) {
+                            issue_kmajor(tmem_base + kColS, k_addr, smem_u32(&sh.q[nstage][0]));
+                            tc_commit(smem_u32(&sh.s_full));
+                        }
+                        __syncwarp();
+                    }
+                    // dQ(t) = dS K  (A = dS^T tile read MN-major, B = K as MN-major), then
+                    // dK += dS^T Q  (A = dS^T tile read K-major, B = Q as MN-major)
+                    ok = mbar_wait(wctx, smem_u32(&sh.ds_ready), ds_cnt & 1u, 12);
+                    if (!ok) break;
+                    ++ds_cnt;
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) {
+                            umma_ss(tmem_base + kColDP,
+                                    make_smem_desc_sw128(ds_addr + ks * 2048, kHalfTileBytes, 1024),
+                                    make_smem_desc_sw128(k_addr + ks * 2048, kHalfTileBytes, 1024),
+                                    idesc_nn, ks > 0 ? 1u : 0u);
+                        }
+                        tc_commit(smem_u32(&sh.dq_full));
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) {
+                            const uint32_t off = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
+                            umma_ss(tmem_base + kColDK, make_smem_desc_sw128(ds_addr + off, 16, 1024),
+                                    make_smem_desc_sw128(q_addr + ks * 2048, kHalfTileBytes, 1024),
+                                    idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
+                        }
+                        tc_commit(smem_u32(&sh.q_empty[stage]));
+                        tc_commit(smem_u32(&sh.ds_empty));
+                        if (!has_next) {
+                            tc_commit(smem_u32(&sh.dkv_full));
+                            tc_commit(smem_u32(&sh.kv_empty));
+                        }
+                    }
+                    __syncwarp();
+                    // dP^T(t+1) = V dO(t+1)^T, once dQ(t) has left tensor memory.
+                    ok = mbar_wait(wctx, smem_u32(&sh.dq_drained), drain_cnt & 1u, 13);
+                    if (!ok) break;
+                    ++drain_cnt;
+                    if (has_next) {
+                        ok = mbar_wait(wctx, smem_u32(&sh.do_full[nstage]), npar, 14);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        if (lane == 0) {
+                            issue_kmajor(tmem_base + kColDP, v_addr, smem_u32(&sh.dout[nstage][0]));
+                            tc_commit(smem_u32(&sh.dp_full));
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+        }
+    } else if (warp >= 8) {
+        // -------------------------------------------------------------------- dQ warpgroup
+        reg_dealloc<72>();
+        const int r = (warp & 3) * 32 + lane;   // query row within the tile
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t dq_tmem = tmem_base + lane_base + kColDP;
+        uint32_t dq_cnt = 0;
+        bool ok = true;
+        for (uint32_t it = 0; ok; ++it) {
+            const uint32_t slot = it & 1u;
+            ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 15);
+            if (!ok) break;
+            const int w = *reinterpret_cast<volatile int*>(&sh.sched_w[slot]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh.sched_empty[slot]));
+            if (w < 0) break;
+            const BwdWork wk = bwd_decode_work(p, w);
+            const int steps = wk.m_count * group;
+            const int pad_tiles = p.padded_q / kTileM;
+            for (int t = 0; t < steps && ok; ++t) {
+                const int hq = wk.head_k * group + t / wk.m_count;
+                const int m = wk.m_first + t % wk.m_count;
+                float* tile = p.dq_accum +
+                              (static_cast<long long>(hq) * pad_tiles + wk.q_pad_begin / kTileM + m) *
+                                  kDqTileFloats;
+                ok = mbar_wait(wctx, smem_u32(&sh.dq_full), dq_cnt & 1u, 16);
+                if (!ok) break;
+                ++dq_cnt;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_x32(dq_tmem + c * 32, v);
+                    tmem_wait_ld();
+                    if (c == 3) {
+                        // All of dQ(t) is in registers: tensor memory may be overwritten.
+                        tc_fence_before_sync();
+                        mbar_arrive(smem_u32(&sh.dq_drained));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float* dst = tile + ((c * 8 + i) * kTileM + r) * 4;
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                     ::"l"(dst), "f"(__uint_as_float(v[4 * i])),
+                                       "f"(__uint_as_float(v[4 * i + 1])),
+                                       "f"(__uint_as_float(v[4 * i + 2])),
+                                       "f"(__uint_as_float(v[4 * i + 3]))
+                                     : "memory");
+                    }
+                }
+            }
+        }
+    } else {
+        // -------------------------------------------------------------------- compute warpgroups
+        reg_alloc<176>();
+        const int wg = warp >> 2;                      // 0: query columns 0-63, 1: 64-127
+        const int i_row = (warp & 3) * 32 + lane;      // key row within the block
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t s_tmem = tmem_base + lane_base + kColS + wg * 64;
+        const uint32_t dp_tmem = tmem_base + lane_base + kColDP + wg * 64;
+        const uint32_t pt_tmem = tmem_base + lane_base + kColS + wg * 64;   // P^T: 32 packed columns
+        const uint32_t ds_row = smem_u32(&sh.ds[0]) + wg * kHalfTileBytes + i_row * 128;
+        const float sl2 = p.scale_log2;
+        uint32_t step_it = 0;
+        uint32_t s_cnt = 0, dp_cnt = 0, dse_cnt = 0, epi_cnt = 0;
+        bool ok = true;
+
+        for (uint32_t it = 0; ok; ++it) {
+            const uint32_t slot = it & 1u;
+            ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 17);
+            if (!ok) break;
+            const int w = *reinterpret_cast<volatile int*>(&sh.sched_w[slot]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh.sched_empty[slot]));
+            if (w < 0) break;
+            const BwdWork wk = bwd_decode_work(p, w);
+            const int steps = wk.m_count * group;
+            const int kv_row = wk.n0 + i_row;
+            const bool kv_valid = kv_row < wk.k_len;
+            const int shift = wk.k_len - wk.q_len;     // key c visible to query r iff c <= r + shift
+
+            for (int t = 0; t < steps && ok; ++t) {
+                const int m = wk.m_first + t % wk.m_count;
+                const uint32_t stage = step_it % kBwdStages;
+                const uint32_t par = (step_it / kBwdStages) & 1u;
+                ++step_it;
+                const int q0 = m * kTileM + wg * 64;   // document-local query row of column 0
+                // Columns c < c_min are hidden from this key row by the causal rule.
+                const int c_min = p.causal ? (kv_row - shift - q0) : 0;
+                const bool need_mask = !kv_valid || c_min > 0;
+
+                // LSE2 / D of this tile arrive with Q.
+                ok = mbar_wait(wctx, smem_u32(&sh.q_full[stage]), par, 18);
+                if (!ok) break;
+                ok = mbar_wait(wctx, smem_u32(&sh.s_full), s_cnt & 1u, 19);
+                if (!ok) break;
+                ++s_cnt;
+                tc_fence_after_sync();
+
+                float pr[64];
+                {
+                    uint32_t a[32], b[32];
+                    tmem_ld_x32(s_tmem, a);
+                    tmem_ld_x32(s_tmem + 32, b);
+                    tmem_wait_ld();
+                    const float4* l2 = reinterpret_cast<const float4*>(&sh.lse2[stage][wg * 64]);
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        const float4 l = l2[g4];
+                        pr[4 * g4 + 0] = fast_exp2(fmaf(__uint_as_float(a[4 * g4 + 0]), sl2, -l.x));
+                        pr[4 * g4 + 1] = fast_exp2(fmaf(__uint_as_float(a[4 * g4 + 1]), sl2, -l.y));
+                        pr[4 * g4 + 2] = fast_exp2(fmaf(__uint_as_float(a[4 * g4 + 2]), sl2, -l.z));
+                        pr[4 * g4 + 3] = fast_exp2(fmaf(__uint_as_float(a[4 * g4 + 3]), sl2, -l.w));
+                    }
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        const float4 l = l2[8 + g4];
+                        pr[32 + 4 * g4 + 0] = fast_exp2(fmaf(__uint_as_float(b[4 * g4 + 0]), sl2, -l.x));
+                        pr[32 + 4 * g4 + 1] = fast_exp2(fmaf(__uint_as_float(b[4 * g4 + 1]), sl2, -l.y));
+                        pr[32 + 4 * g4 + 2] = fast_exp2(fmaf(__uint_as_float(b[4 * g4 + 2]), sl2, -l.z));
+                        pr[32 + 4 * g4 + 3] = fast_exp2(fmaf(__uint_as_float(b[4 * g4 + 3]), sl2, -l.w));
+                    }
+                }
+                if (need_mask) {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        if (!kv_valid || c < c_min) pr[c] = 0.f;
+                    }
+                }
+                {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) pk[c] = pack_bf16x2(pr[2 * c], pr[2 * c + 1]);
+                    tmem_st_x32(pt_tmem, pk);
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(smem_u32(&sh.p_ready));
+                }
+
+                // dS^T = P^T * (dP^T - D)
+                ok = mbar_wait(wctx, smem_u32(&sh.dp_full), dp_cnt & 1u, 20);
+                if (!ok) break;
+                ++dp_cnt;
+                tc_fence_after_sync();
+                uint32_t dsp[32];
+                {
+                    uint32_t a[32], b[32];
+                    tmem_ld_x32(dp_tmem, a);
+                    tmem_ld_x32(dp_tmem + 32, b);
+                    tmem_wait_ld();
+                    const float4* dsum = reinterpret_cast<const float4*>(&sh.dpsum[stage][wg * 64]);
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        const float4 d = dsum[g4];
+                        const float x0 = pr[4 * g4 + 0] * (__uint_as_float(a[4 * g4 + 0]) - d.x);
+                        const float x1 = pr[4 * g4 + 1] * (__uint_as_float(a[4 * g4 + 1]) - d.y);
+                        const float x2 = pr[4 * g4 + 2] * (__uint_as_float(a[4 * g4 + 2]) - d.z);
+                        const float x3 = pr[4 * g4 + 3] * (__uint_as_float(a[4 * g4 + 3]) - d.w);
+                        dsp[2 * g4] = pack_bf16x2(x0, x1);
+                        dsp[2 * g4 + 1] = pack_bf16x2(x2, x3);
+                    }
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        const float4 d = dsum[8 + g4];
+                        const float x0 = pr[32 + 4 * g4 + 0] * (__uint_as_float(b[4 * g4 + 0]) - d.x);
+                        const float x1 = pr[32 + 4 * g4 + 1] * (__uint_as_float(b[4 * g4 + 1]) - d.y);
+                        const float x2 = pr[32 + 4 * g4 + 2] * (__uint_as_float(b[4 * g4 + 2]) - d.z);
+                        const float x3 = pr[32 + 4 * g4 + 3] * (__uint_as_float(b[4 * g4 + 3]) - d.w);
+                        dsp[16 + 2 * g4] = pack_bf16x2(x0, x1);
+                        dsp[16 + 2 * g4 + 1] = pack_bf16x2(x2, x3);
+                    }
+                }
+                // The previous step's dK / dQ MMAs must be done with the dS^T tile.
+                ok = mbar_wait(wctx, smem_u32(&sh.ds_empty), (dse_cnt & 1u) ^ 1u, 21);
+                if (!ok) break;
+                ++dse_cnt;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    const uint32_t addr = ds_row + ((ch ^ (i_row & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(addr), "r"(dsp[4 * ch]), "r"(dsp[4 * ch + 1]),
+                                   "r"(dsp[4 * ch + 2]), "r"(dsp[4 * ch + 3])
+                                 : "memory");
+                }
+                fence_proxy_async_smem();
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&sh.ds_ready));
+            }
+            if (!ok) break;
+
+            // Epilogue: warpgroup 0 writes dV, warpgroup 1 writes dK * scale.
+            __nv_bfloat16* dst_base = (wg == 0 ? p.dv : p.dk) +
+                                      ((static_cast<long long>(wk.k_begin) + kv_row) * p.heads_k +
+                                       wk.head_k) * kHeadDim;
+            const float mul = wg == 0 ? 1.f : p.scale;
+            if (steps > 0) {
+                ok = mbar_wait(wctx, smem_u32(&sh.dkv_full), epi_cnt & 1u, 22);
+                if (!ok) break;
+                ++epi_cnt;
+                tc_fence_after_sync();
+            }
+            const uint32_t acc_tmem = tmem_base + lane_base + (wg == 0 ? kColDV : kColDK);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                if (steps > 0) {
+                    tmem_ld_x32(acc_tmem + c * 32, v);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0u;
+                }
+                if (kv_valid) {
+                    uint4* dst = reinterpret_cast<uint4*>(dst_base + c * 32);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            o[e] = pack_bf16x2(__uint_as_float(v[q4 * 8 + 2 * e]) * mul,
+                                               __uint_as_float(v[q4 * 8 + 2 * e + 1]) * mul);
+                        }
+                        dst[q4] = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+            if (steps > 0) {
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&sh.dkv_empty));
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 12) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Preprocess: one warp per query row.  D = sum_d dO * O, LSE2 = LSE * log2(e) with -inf and
+// padding rows mapped to +inf (their P becomes exactly 0).  Also zeroes dq_accum.
+// ---------------------------------------------------------------------------------------
+struct BwdPreParams {
+    const __nv_bfloat16* o;
+    const __nv_bfloat16* dout;
+    const float* lse;
+    float* lse2;
+    float* dpsum;
+    const int* cu_seqlens_q;
+    int batch;
+    int seqlen_q;
+    int heads_q;
+    int padded_q;
+    long long lse_head_stride;
+    long long lse_batch_stride;
+};
+
+__global__ void __launch_bounds__(256)
+bwd_preprocess_kernel(const BwdPreParams p) {
+    // grid: (padded_q / 8, heads_q); 8 warps per CTA, one padded row per warp.
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int prow = blockIdx.x * 8 + warp;
+    const int h = blockIdx.y;
+    if (prow >= p.padded_q) return;
+
+    // Locate the document that owns this padded row.
+    int doc = -1, q_begin = 0, q_len = 0, pad_begin = 0;
+    if (p.cu_seqlens_q == nullptr) {
+        const int per = ((p.seqlen_q + 127) / 128) * 128;
+        doc = prow / per;
+        pad_begin = doc * per;
+        q_begin = doc * p.seqlen_q;
+        q_len = p.seqlen_q;
+        if (doc >= p.batch) doc = -1;
+    } else {
+        // Binary search over padded begins (monotone in doc).
+        int lo = 0, hi = p.batch - 1;
+        while (lo < hi) {
+            int mid = (lo + hi + 1) >> 1;
+            if (bwd_padded_begin(p.cu_seqlens_q[mid], mid) <= prow) lo = mid; else hi = mid - 1;
+        }
+        doc = lo;
+        q_begin = p.cu_seqlens_q[doc];
+        q_len = p.cu_seqlens_q[doc + 1] - q_begin;
+        pad_begin = bwd_padded_begin(q_begin, doc);
+        if (prow < pad_begin) doc = -1;
+    }
+    const int r = prow - pad_begin;
+    const long long out_idx = static_cast<long long>(h) * p.padded_q + prow;
+    float d = 0.f;
+    float l2 = INFINITY;
+    if (doc >= 0 && r < q_len) {
+        const long long tok = static_cast<long long>(q_begin) + r;
+        const long long base = (tok * p.heads_q + h) * kHeadDim + lane * 4;
+        const uint2 ov = *reinterpret_cast<const uint2*>(p.o + base);
+        const uint2 gv = *reinterpret_cast<const uint2*>(p.dout + base);
+        const float o0 = __uint_as_float(ov.x << 16), o1 = __uint_as_float(ov.x & 0xFFFF0000u);
+        const float o2 = __uint_as_float(ov.y << 16), o3 = __uint_as_float(ov.y & 0xFFFF0000u);
+        const float g0 = __uint_as_float(gv.x << 16), g1 = __uint_as_float(gv.x & 0xFFFF0000u);
+        const float g2 = __uint_as_float(gv.y << 16), g3 = __uint_as_float(gv.y & 0xFFFF0000u);
+        d = o0 * g0 + o1 * g1 + o2 * g2 + o3 * g3;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, off);
+        long long lse_idx;
+        if (p.cu_seqlens_q == nullptr) {
+            lse_idx = static_cast<long long>(doc) * p.lse_batch_stride +
+                      static_cast<long long>(h) * p.lse_head_stride + r;
+        } else {
+            lse_idx = static_cast<long long>(h) * p.lse_head_stride + tok;
+        }
+        const float l = p.lse[lse_idx];
+        l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+    }
+    if (lane == 0) {
+        p.lse2[out_idx] = l2;
+        p.dpsum[out_idx] = d;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Postprocess: dQ = bf16(scale * dq_accum), un-tiling the accumulator layout.
+// One CTA of 128 threads per (head, padded query tile).
+// ---------------------------------------------------------------------------------------
+struct BwdPostParams {
+    const float* dq_accum;
+    __nv_bfloat16* dq;
+    const int* cu_seqlens_q;
+    int batch;
+    int seqlen_q;
+    int heads_q;
+    int padded_q;
+    float scale;
+};
+
+__global__ void __launch_bounds__(128)
+bwd_postprocess_kernel(const BwdPostParams p) {
+    __shared__ float tile[kTileM][64 + 4];
+    const int pad_tile = blockIdx.x;
+    const int h = blockIdx.y;
+    const int pad_tiles = p.padded_q / kTileM;
+    const int prow0 = pad_tile * kTileM;
+
+    int doc = -1, q_begin = 0, q_len = 0, pad_begin = 0;
+    if (p.cu_seqlens_q == nullptr) {
+        const int per = ((p.seqlen_q + 127) / 128) * 128;
+        doc = prow0 / per;
+        pad_begin = doc * per;
+        q_begin = doc * p.seqlen_q;
+        q_len = p.seqlen_q;
+        if (doc >= p.batch) return;
+    } else {
+        int lo = 0, hi = p.batch - 1;
+        while (lo < hi) {
+            int mid = (lo + hi + 1) >> 1;
+            if (bwd_padded_begin(p.cu_seqlens_q[mid], mid) <= prow0) lo = mid; else hi = mid - 1;
+        }
+        doc = lo;
+        q_begin = p.cu_seqlens_q[doc];
+        q_len = p.cu_seqlens_q[doc + 1] - q_begin;
+        pad_begin = bwd_padded_begin(q_begin, doc);
+        if (prow0 < pad_begin) return;
+    }
+    const int r0 = prow0 - pad_begin;
+    if (r0 >= q_len) return;
+
+    const float4* src = reinterpret_cast<const float4*>(
+        p.dq_accum + (static_cast<long long>(h) * pad_tiles + pad_tile) * kDqTileFloats);
+    // src[chunk * 128 + row] holds columns 4*chunk .. 4*chunk+3 of `row`.  Two passes of 64
+    // columns each keep the transposition buffer inside static shared memory.
+    const int sub = threadIdx.x & 7;
+    for (int half = 0; half < 2; ++half) {
+        for (int chunk = 0; chunk < 16; ++chunk) {
+            const float4 v = src[(half * 16 + chunk) * kTileM + threadIdx.x];
+            float* dst = &tile[threadIdx.x][chunk * 4];
+            dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+        }
+        __syncthreads();
+        // 8 threads x 16 bytes cover the 128-byte half row; 16 rows per pass.
+        for (int rr = threadIdx.x >> 3; rr < kTileM; rr += 16) {
+            if (r0 + rr < q_len) {
+                const float* sp = &tile[rr][sub * 8];
+                uint4 o;
+                o.x = pack_bf16x2(sp[0] * p.scale, sp[1] * p.scale);
+                o.y = pack_bf16x2(sp[2] * p.scale, sp[3] * p.scale);
+                o.z = pack_bf16x2(sp[4] * p.scale, sp[5] * p.scale);
+                o.w = pack_bf16x2(sp[6] * p.scale, sp[7] * p.scale);
+                const long long tok = static_cast<long long>(q_begin) + r0 + rr;
+                *reinterpret_cast<uint4*>(p.dq + (tok * p.heads_q + h) * kHeadDim + half * 64 +
+                                          sub * 8) = o;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace b2a
