@@ -1,0 +1,172 @@
+"""Backward parity on the GPU: dQ, dK, dV from the CUDA path (through min_fa3_op -> C ABI)
+against the fp32 autograd oracle and the reference's golden fixtures.  Acceptance: each
+gradient within 2x the max-abs error of a bf16 PyTorch attention against the oracle."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import min_fa3_op
+from conftest import from_bf16_bits, load_golden
+from gpu_util import assert_within, bound, make_bshd, make_varlen, varlen_bf16_errors
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def fwd_bwd_bshd(q, k, v, dout, causal, **kw):
+    qc, kc, vc, dc = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
+    out, lse = min_fa3_op.forward(qc, kc, vc, causal, return_lse=True)
+    grads = min_fa3_op.backward(dc, qc, kc, vc, out, lse, causal, **kw)
+    torch.cuda.synchronize()
+    return out, lse, grads
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("b,s,qh,kvh", [
+    (1, 128, 32, 32),      # reference backward test default
+    (1, 129, 4, 2),
+    (2, 1024, 16, 4),      # BASELINE config 1
+    (1, 333, 2, 1),
+    (2, 640, 8, 8),
+    (1, 1, 2, 2),
+])
+def test_bshd_backward_vs_oracle(b, s, qh, kvh, causal):
+    q, k, v, dout = make_bshd(4321 + s, b, s, qh, kvh)
+    _, _, (dq, dk, dv) = fwd_bwd_bshd(q, k, v, dout, causal)
+    assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
+    rq, rk, rv = orc.bshd_backward(q, k, v, dout, causal)
+    e = orc.bf16_attention_error(q, k, v, causal, dout)
+    assert_within("dQ", dq, rq, e["dq"])
+    assert_within("dK", dk, rk, e["dk"])
+    assert_within("dV", dv, rv, e["dv"])
+
+
+@pytest.mark.parametrize("sq,sk", [(256, 512), (300, 200)])
+def test_bshd_backward_rectangular_causal(sq, sk):
+    q, k, v, dout = make_bshd(5, 1, sq, 4, 2, sk=sk)
+    _, _, (dq, dk, dv) = fwd_bwd_bshd(q, k, v, dout, True)
+    rq, rk, rv = orc.bshd_backward(q, k, v, dout, True)
+    e = orc.bf16_attention_error(q, k, v, True, dout)
+    assert_within("dQ", dq, rq, e["dq"])
+    assert_within("dK", dk, rk, e["dk"])
+    assert_within("dV", dv, rv, e["dv"])
+
+
+@pytest.mark.parametrize("tag,causal", [("full", False), ("causal", True)])
+def test_bshd_backward_golden(tag, causal):
+    g = load_golden(f"bshd_{tag}")
+    q, k, v, dout = (from_bf16_bits(g[n]) for n in ("q", "k", "v", "dout"))
+    _, _, grads = fwd_bwd_bshd(q, k, v, dout, causal)
+    e = orc.bf16_attention_error(q, k, v, causal, dout)
+    for ours, name in zip(grads, ("dq", "dk", "dv")):
+        assert_within(name, ours, torch.from_numpy(g[name]), e[name])
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("lengths,qh,kvh", [
+    ([128, 129], 4, 2),
+    ([128, 111, 94, 128, 111, 94], 8, 2),       # S - 17*(i%3), the reference's uneven case
+    ([1, 700, 255, 257, 1024, 3], 4, 4),
+    ([37] * 40, 2, 2),
+])
+def test_varlen_backward_vs_oracle(lengths, qh, kvh, causal):
+    q, k, v, dout, cu = make_varlen(7 + len(lengths), lengths, qh, kvh)
+    qc, kc, vc, dc, cuc = q.cuda(), k.cuda(), v.cuda(), dout.cuda(), cu.cuda()
+    out, lse = min_fa3_op.forward_varlen(qc, kc, vc, cuc, cuc, max(lengths), max(lengths), causal,
+                                         cu_seqlens_q_host=cu, cu_seqlens_k_host=cu, return_lse=True)
+    dq, dk, dv = min_fa3_op.backward_varlen(dc, qc, kc, vc, out, lse, cuc, cuc, max(lengths),
+                                            max(lengths), causal)
+    torch.cuda.synchronize()
+    rq, rk, rv = orc.varlen_backward(q, k, v, dout, cu.tolist(), cu.tolist(), causal)
+    e = varlen_bf16_errors(q, k, v, dout, cu, causal)
+    assert_within("dQ", dq, rq, e["dq"])
+    assert_within("dK", dk, rk, e["dk"])
+    assert_within("dV", dv, rv, e["dv"])
+
+
+@pytest.mark.parametrize("tag,causal", [("full", False), ("causal", True)])
+def test_varlen_backward_golden(tag, causal):
+    g = load_golden(f"varlen_{tag}")
+    q, k, v, dout = (from_bf16_bits(g[n]) for n in ("q", "k", "v", "dout"))
+    cu = torch.from_numpy(g["cu_seqlens"])
+    lengths = (cu[1:] - cu[:-1]).tolist()
+    qc, kc, vc, dc, cuc = q.cuda(), k.cuda(), v.cuda(), dout.cuda(), cu.cuda()
+    out, lse = min_fa3_op.forward_varlen(qc, kc, vc, cuc, cuc, max(lengths), max(lengths), causal,
+                                         cu_seqlens_q_host=cu, cu_seqlens_k_host=cu, return_lse=True)
+    grads = min_fa3_op.backward_varlen(dc, qc, kc, vc, out, lse, cuc, cuc, max(lengths),
+                                       max(lengths), causal)
+    e = varlen_bf16_errors(q, k, v, dout, cu, causal)
+    for ours, name in zip(grads, ("dq", "dk", "dv")):
+        assert_within(name, ours, torch.from_numpy(g[name]), e[name])
+
+
+def test_backward_writes_into_caller_buffers():
+    # reference: scripts/test_min_fa3/test_min_fa3_backward.py:60-75
+    q, k, v, dout = make_bshd(8, 1, 256, 4, 2)
+    qc, kc, vc, dc = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
+    out, lse = min_fa3_op.forward(qc, kc, vc, True, return_lse=True)
+    expected = min_fa3_op.backward(dc, qc, kc, vc, out, lse, True)
+    buffers = (torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc))
+    got = min_fa3_op.backward(dc, qc, kc, vc, out, lse, True, dq=buffers[0], dk=buffers[1],
+                              dv=buffers[2])
+    assert all(r.data_ptr() == b.data_ptr() for r, b in zip(got, buffers))
+    for a, b, name in zip(got, expected, ("dq", "dk", "dv")):
+        # dK / dV are accumulated in a fixed order; dQ uses fp32 atomics (order may vary)
+        if name == "dq":
+            assert (a.float() - b.float()).abs().max().item() <= 2.0 ** -6
+        else:
+            assert torch.equal(a, b), name
+
+
+def test_backward_rejects_bad_lse_shape():
+    # reference: scripts/test_min_fa3/test_min_fa3_backward.py:95-103
+    q, k, v, dout = make_bshd(9, 1, 128, 4, 2)
+    qc, kc, vc, dc = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
+    out, lse = min_fa3_op.forward(qc, kc, vc, True, return_lse=True)
+    bad = torch.empty((1, 4, 129), device="cuda", dtype=torch.float32)
+    with pytest.raises(RuntimeError, match=r"softmax_lse must have shape \[B, QH, Sq\]"):
+        min_fa3_op.backward(dc, qc, kc, vc, out, bad, True)
+    with pytest.raises(RuntimeError, match="dq must have shape"):
+        min_fa3_op.backward(dc, qc, kc, vc, out, lse, True, dq=torch.empty_like(kc))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_full_size_backward_properties(causal):
+    """Config 2 (B=4, S=8192, QH=32, KVH=8).  Size-independent identities of softmax attention:
+    sum_k dV[k] = sum_q dO[q] per KV head (rows of P sum to one), and
+    sum_i q_i . dq_i = sum_j k_j . dk_j per KV head (S depends on q and k only through q.k)."""
+    torch.manual_seed(1)
+    b, s, qh, kvh = 4, 8192, 32, 8
+    q = torch.randn(b, s, qh, 128, device="cuda").to(torch.bfloat16)
+    k = torch.randn(b, s, kvh, 128, device="cuda").to(torch.bfloat16)
+    v = torch.randn(b, s, kvh, 128, device="cuda").to(torch.bfloat16)
+    dout = torch.randn(b, s, qh, 128, device="cuda").to(torch.bfloat16)
+    out, lse = min_fa3_op.forward(q, k, v, causal, return_lse=True)
+    dq, dk, dv = min_fa3_op.backward(dout, q, k, v, out, lse, causal)
+    for t in (dq, dk, dv):
+        assert torch.isfinite(t.float()).all()
+
+    g = qh // kvh
+    dv_sum = dv.float().sum(dim=1)                                        # [B, KVH, D]
+    do_sum = dout.float().view(b, s, kvh, g, 128).sum(dim=(1, 3))         # [B, KVH, D]
+    scale = do_sum.abs().max().item()
+    assert (dv_sum - do_sum).abs().max().item() <= 2e-2 * scale
+
+    qdq = (q.float() * dq.float()).view(b, s, kvh, g, 128).sum(dim=(1, 3, 4))   # [B, KVH]
+    kdk = (k.float() * dk.float()).sum(dim=(1, 3))                              # [B, KVH]
+    denom = (q.float() * dq.float()).abs().view(b, s, kvh, g, 128).sum(dim=(1, 3, 4))
+    assert ((qdq - kdk).abs() / denom).max().item() <= 2e-3
+
+    # one KV head group of batch 0, first 1024 keys/queries of a causal problem, is itself a
+    # complete attention problem: check it against the fp32 oracle
+    if causal:
+        n = 512
+        qs, ks, vs, ds = (t[:1, :n].contiguous() for t in (q, k, v, dout))
+        o2, l2 = min_fa3_op.forward(qs, ks, vs, True, return_lse=True)
+        g2 = min_fa3_op.backward(ds, qs, ks, vs, o2, l2, True)
+        # dQ of the prefix equals dQ of the full problem (rows < n only see keys < n)
+        assert (g2[0].float() - dq[:1, :n].float()).abs().max().item() <= 3e-2
+        rq, rk, rv = orc.bshd_backward(qs[:, :, :4].cpu(), ks[:, :, :1].cpu(), vs[:, :, :1].cpu(),
+                                       ds[:, :, :4].cpu(), True)
+        assert (g2[0][:, :, :4].float().cpu() - rq).abs().max().item() <= 3e-2
