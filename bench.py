@@ -1,0 +1,358 @@
+"""Benchmark of the attention hot path: forward + backward on synthetic inputs.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU attention
+
+One step is one forward + backward pass over the workload.  At every N the workload is
+BASELINE config 2 per GPU (BSHD, causal, B=4, S=8192, QH=32, KVH=8, d=128, bf16 N(0,1)
+from a fixed seed): each rank owns an independent batch, there is no data-path collective,
+scaling is weak.  Printed numbers use the causal-discounted algorithmic FLOPs
+``14 * QH * D * sum_docs L(L+1)/2`` per step (forward 4x, backward 10x).
+
+The JSON line carries: ``value`` (whole-job TFLOPS with inputs resident in HBM, CUDA events,
+max over ranks), ``e2e`` (same metric through ``min_fa3_op`` with pinned host buffers copied
+in and results copied out inside the timed region), ``roofline`` (dominant kernel = the
+backward main kernel, timed live with CUDA events around each launch), ``cpu_baseline``
+(fp32 PyTorch SDPA forward + autograd backward on the host cores, a bounded sample) and
+``clocks`` sampled with nvidia-smi during the timed region.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = dict(name="bshd_causal_B4_S8192_QH32_KVH8_D128", batch=4, seqlen=8192, heads_q=32,
+                heads_k=8, head_dim=128, causal=True)
+METRIC = "fwd+bwd attention TFLOPS (causal FLOPs), whole job; per-GPU value and % of bf16 peak alongside"
+UNIT = "TFLOPS"
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def step_flops(w=WORKLOAD):
+    s = w["seqlen"]
+    vis = s * (s + 1) / 2 if w["causal"] else float(s) * s
+    unit = w["heads_q"] * w["head_dim"] * vis * w["batch"]
+    return 4.0 * unit, 10.0 * unit
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return float(data["bf16_tflops"]), float(data.get("bf16_tflops_sustained", 0.0)), "measured"
+    return FALLBACK_BF16_TFLOPS, 1400.0, "fallback"
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons in the background."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        sm, sm_max, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for parts in self.samples:
+            try:
+                sm.append(float(parts[0]))
+                sm_max.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(sm_max) if sm_max else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+# CPU baseline / reference arm
+# --------------------------------------------------------------------------------------
+def cpu_attention_sample(seconds_budget: float, seed: int = 0):
+    """Times the reference's CPU-capable attention (fp32 SDPA + autograd backward,
+    scripts/test_min_fa3/test_min_fa3_backward.py:16-36) on KV-head groups of the workload:
+    one group = one batch element, one KV head and its QH/KVH query heads at full S.
+    Returns (TFLOPS, groups timed, seconds)."""
+    import torch.nn.functional as F
+
+    w = WORKLOAD
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = w["heads_q"] // w["heads_k"]
+    gen = torch.Generator().manual_seed(seed)
+    s = w["seqlen"]
+    fwd, bwd = step_flops()
+    group_flops = (fwd + bwd) / (w["batch"] * w["heads_k"])
+    done, t0 = 0, time.perf_counter()
+    while True:
+        q = torch.randn(1, g, s, 128, generator=gen).to(torch.bfloat16).float().requires_grad_()
+        k = torch.randn(1, 1, s, 128, generator=gen).to(torch.bfloat16).float().requires_grad_()
+        v = torch.randn(1, 1, s, 128, generator=gen).to(torch.bfloat16).float().requires_grad_()
+        dout = torch.randn(1, g, s, 128, generator=gen).to(torch.bfloat16).float()
+        if done == 0:
+            t0 = time.perf_counter()   # exclude the first input generation
+        out = F.scaled_dot_product_attention(q, k, v, is_causal=w["causal"], enable_gqa=g != 1)
+        torch.autograd.grad(out, (q, k, v), dout)
+        done += 1
+        elapsed = time.perf_counter() - t0
+        if elapsed >= seconds_budget or done >= w["batch"] * w["heads_k"]:
+            break
+    return done * group_flops / elapsed / 1e12, done, elapsed
+
+
+def cpu_baseline_record(seconds_budget: float) -> dict:
+    tflops, groups, secs = cpu_attention_sample(seconds_budget)
+    w = WORKLOAD
+    return {"value": tflops, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": f"{groups} of {w['batch'] * w['heads_k']} (batch, KV-head) groups of the workload "
+                      f"(each {w['heads_q'] // w['heads_k']} query heads x 1 KV head, S={w['seqlen']}, causal), "
+                      f"fp32 torch SDPA forward + autograd backward, {secs:.1f} s"}
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    for _ in range(min(args.warmup, 1)):
+        cpu_attention_sample(2.0)
+    values, t0 = [], time.perf_counter()
+    per_step_budget = max(2.0, min(10.0, 90.0 / max(args.steps, 1)))
+    samples = []
+    for _ in range(args.steps):
+        tflops, groups, secs = cpu_attention_sample(per_step_budget)
+        values.append(tflops)
+        samples.append((groups, secs))
+    value = statistics.mean(values)
+    fwd, bwd = step_flops()
+    w = WORKLOAD
+    sample = (f"each step: {samples[0][0]} of {w['batch'] * w['heads_k']} (batch, KV-head) groups, fp32 torch SDPA "
+              f"forward + autograd backward on CPU, ~{per_step_budget:.0f} s; value = mean over steps")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": (fwd + bwd) / (value * 1e12) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "note": "ms_per_step extrapolates the sampled rate to the full workload"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# CUDA arm
+# --------------------------------------------------------------------------------------
+def run_cuda_arm(args) -> None:
+    import torch.distributed as dist
+
+    import min_fa3_op
+    from min_fa3_demo_b200 import _cabi
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _cabi.load()   # raises if the CUDA library is missing
+
+    w = WORKLOAD
+    b, s, qh, kvh = w["batch"], w["seqlen"], w["heads_q"], w["heads_k"]
+    causal = w["causal"]
+    gen = torch.Generator(device="cpu").manual_seed(1000 * 0 + rank)
+    host = {}
+    for name, heads in (("q", qh), ("k", kvh), ("v", kvh), ("dout", qh)):
+        t = torch.empty(b, s, heads, 128, dtype=torch.bfloat16).pin_memory()
+        t.copy_(torch.randn(b, s, heads, 128, generator=gen).to(torch.bfloat16))
+        host[name] = t
+    q, k, v, dout = (host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "dout"))
+    torch.cuda.synchronize()
+
+    def step_resident():
+        out, lse = min_fa3_op.forward(q, k, v, causal, return_lse=True)
+        return out, min_fa3_op.backward(dout, q, k, v, out, lse, causal)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    fwd_flops, bwd_flops = step_flops()
+    flops = fwd_flops + bwd_flops
+
+    # ---- device-resident timing -------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    barrier()
+    lib.b2a_profile_enable(1)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_resident()
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    buf = (ctypes.c_float * 256)()
+    n_bwd = lib.b2a_profile_read(1, buf, 256)
+    bwd_ms = [buf[i] for i in range(n_bwd)]
+    n_fwd = lib.b2a_profile_read(0, buf, 256)
+    fwd_ms = [buf[i] for i in range(n_fwd)]
+    lib.b2a_profile_enable(0)
+    t = torch.tensor([ms_total], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = t.item() / args.steps
+
+    # ---- end to end through the public API with host buffers ---------------------------
+    out_host = {n: torch.empty_like(host[n]).pin_memory() for n in ("q", "k", "v")}
+    o_host = torch.empty_like(host["q"]).pin_memory()
+
+    def step_e2e():
+        qd, kd, vd, dd = (host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "dout"))
+        out, lse = min_fa3_op.forward(qd, kd, vd, causal, return_lse=True)
+        dq, dk, dv = min_fa3_op.backward(dd, qd, kd, vd, out, lse, causal)
+        o_host.copy_(out, non_blocking=True)
+        out_host["q"].copy_(dq, non_blocking=True)
+        out_host["k"].copy_(dk, non_blocking=True)
+        out_host["v"].copy_(dv, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = t.item() / e2e_steps
+    h2d = sum(host[n].numel() * 2 for n in ("q", "k", "v", "dout"))
+    d2h = o_host.numel() * 2 + sum(out_host[n].numel() * 2 for n in ("q", "k", "v"))
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    burst, sustained, peak_kind = measured_peaks()
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    bwd_avg_ms = statistics.mean(bwd_ms) if bwd_ms else None
+    achieved = bwd_flops / (bwd_avg_ms * 1e-3) / 1e12 if bwd_avg_ms else None
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["name"], "batch_per_gpu": b, "seq_len": s, "heads_q": qh,
+                   "heads_k": kvh, "head_dim": 128, "causal": causal,
+                   "parallelism": f"{world} independent replica(s), no data-path collective",
+                   "l2": "inputs larger than L2 (1.7 GB of tensors per step vs 126 MB L2)",
+                   "flops_per_step_per_gpu": flops},
+        "tflops_per_gpu": value / world,
+        "pct_of_bf16_peak": {f"{peak_kind}_burst": 100.0 * value / world / burst,
+                             f"{peak_kind}_sustained": 100.0 * value / world / sustained if sustained else None,
+                             "nominal_dense_2250": 100.0 * value / world / NOMINAL_BF16_TFLOPS},
+        "kernel_ms": {"fwd_kernel": statistics.mean(fwd_ms) if fwd_ms else None,
+                      "bwd_kernel": bwd_avg_ms,
+                      "fwd_tflops": fwd_flops / (statistics.mean(fwd_ms) * 1e-3) / 1e12 if fwd_ms else None},
+        "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": achieved, "peak": sustained or burst,
+                     "peak_kind": f"{peak_kind} sustained cuBLAS bf16 (kernel timed inside a long step)",
+                     "unit": "TFLOP/s", "frac": achieved / (sustained or burst) if achieved else None,
+                     "frac_of_burst": achieved / burst if achieved else None,
+                     "traffic": None},
+        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 4 * args.steps,
+        "gpu_launches_note": "per step: fwd_kernel, bwd_preprocess_kernel, bwd_kernel, bwd_postprocess_kernel",
+        "clocks": clocks,
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline_record(args.cpu_seconds)
+    traffic_file = ROOT / "profiles" / "bwd_kernel_traffic.json"
+    if traffic_file.exists():
+        line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get("dram_bytes_per_launch")
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("cuda", "reference"), default="cuda")
+    parser.add_argument("--cpu-seconds", type=float, default=15.0,
+                        help="time budget of the CPU baseline sample (N=1 only)")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_cuda_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -135,6 +135,28 @@ int b2a_bwd(const b2a_bwd_args* args, void* cuda_stream);
  */
 int b2a_check_status(const void* workspace, void* cuda_stream);
 
+/* ------------------------------------------------------------------------- */
+/* Kernel timing                                                              */
+/* ------------------------------------------------------------------------- */
+
+#define B2A_KERNEL_FWD 0
+#define B2A_KERNEL_BWD 1
+
+/*
+ * While enabled (per calling thread), every launch of the forward / backward main kernel
+ * is bracketed by CUDA events on the launch stream; up to 256 launches per kernel are kept.
+ * Enabling resets the record.  No counterpart in the reference (its scripts time whole
+ * calls, ring_test/benchmark_topology_forward.py:382-411).
+ */
+int b2a_profile_enable(int enable);
+
+/*
+ * Synchronises the recorded events and writes the duration in milliseconds of each recorded
+ * launch of `kernel` (B2A_KERNEL_*) to ms[0..]; returns the number written (<= capacity) or
+ * a negative error code.
+ */
+int b2a_profile_read(int kernel, float* ms, int capacity);
+
 #ifdef __cplusplus
 }
 #endif

@@ -90,6 +90,8 @@ SIGNATURES = {
     "b2a_bwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b2a_bwd": (c_int32, [POINTER(BwdArgs), c_void_p]),
     "b2a_check_status": (c_int32, [c_void_p, c_void_p]),
+    "b2a_profile_enable": (c_int32, [c_int32]),
+    "b2a_profile_read": (c_int32, [c_int32, POINTER(c_float), c_int32]),
 }
 
 _lib = None

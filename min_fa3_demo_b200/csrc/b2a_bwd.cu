@@ -198,7 +198,9 @@ int b2a_bwd(const b2a_bwd_args* a, void* cuda_stream) {
     int grid = a->grid_blocks > 0 ? a->grid_blocks : dev.sm_count;
     if (work_items < grid) grid = static_cast<int>(work_items);
     if (grid < 1) grid = 1;
+    profile_mark(B2A_KERNEL_BWD, false, stream);
     bwd_kernel<<<grid, kBwdThreads, kBwdSmemBytes, stream>>>(map_q, map_k, map_v, map_do, p);
+    profile_mark(B2A_KERNEL_BWD, true, stream);
     B2A_CUDA_OK(cudaGetLastError());
 
     // Postprocess.

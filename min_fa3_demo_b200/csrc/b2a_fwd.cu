@@ -131,12 +131,15 @@ int b2a_fwd(const b2a_fwd_args* a, void* cuda_stream) {
     if (p.merge) {
         rc = configure_fwd_kernel<true>(dev);
         if (rc != B2A_OK) return rc;
+        profile_mark(B2A_KERNEL_FWD, false, stream);
         fwd_kernel<true><<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(map_q, map_k, map_v, p);
     } else {
         rc = configure_fwd_kernel<false>(dev);
         if (rc != B2A_OK) return rc;
+        profile_mark(B2A_KERNEL_FWD, false, stream);
         fwd_kernel<false><<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(map_q, map_k, map_v, p);
     }
+    profile_mark(B2A_KERNEL_FWD, true, stream);
     B2A_CUDA_OK(cudaGetLastError());
     return B2A_OK;
 }

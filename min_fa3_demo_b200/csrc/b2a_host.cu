@@ -99,9 +99,58 @@ int make_token_map(CUtensorMap* map, const void* base, uint64_t tokens, uint64_t
     return B2A_OK;
 }
 
+namespace {
+
+constexpr int kProfileSlots = 256;
+
+struct ProfileState {
+    bool enabled = false;
+    int count[2] = {0, 0};
+    cudaEvent_t start[2][kProfileSlots] = {};
+    cudaEvent_t stop[2][kProfileSlots] = {};
+};
+
+ProfileState& profile_state() {
+    static thread_local ProfileState st;
+    return st;
+}
+
+}  // namespace
+
+void profile_mark(int kernel, bool after, cudaStream_t stream) {
+    ProfileState& st = profile_state();
+    if (!st.enabled || kernel < 0 || kernel > 1) return;
+    int idx = st.count[kernel];
+    if (idx >= kProfileSlots) return;
+    cudaEvent_t* ev = after ? &st.stop[kernel][idx] : &st.start[kernel][idx];
+    if (*ev == nullptr && cudaEventCreate(ev) != cudaSuccess) return;
+    cudaEventRecord(*ev, stream);
+    if (after) st.count[kernel] = idx + 1;
+}
+
 }  // namespace b2a
 
 extern "C" {
+
+int b2a_profile_enable(int enable) {
+    b2a::ProfileState& st = b2a::profile_state();
+    st.enabled = enable != 0;
+    st.count[0] = st.count[1] = 0;
+    return B2A_OK;
+}
+
+int b2a_profile_read(int kernel, float* ms, int capacity) {
+    using namespace b2a;
+    B2A_REQUIRE(kernel == 0 || kernel == 1, "kernel must be B2A_KERNEL_FWD or B2A_KERNEL_BWD");
+    B2A_REQUIRE(ms != nullptr && capacity >= 0, "ms must not be NULL");
+    ProfileState& st = profile_state();
+    int n = st.count[kernel] < capacity ? st.count[kernel] : capacity;
+    for (int i = 0; i < n; ++i) {
+        B2A_CUDA_OK(cudaEventSynchronize(st.stop[kernel][i]));
+        B2A_CUDA_OK(cudaEventElapsedTime(&ms[i], st.start[kernel][i], st.stop[kernel][i]));
+    }
+    return n;
+}
 
 int b2a_abi_version(void) { return 1; }
 

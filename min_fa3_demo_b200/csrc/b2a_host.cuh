@@ -73,4 +73,9 @@ int launch_varlen_plan(int kind, const int* cu_seqlens_q, const int* cu_seqlens_
                        int causal, int2* work_list, int* num_entries, int max_entries_cap,
                        cudaStream_t stream);
 
+// Optional per-thread kernel timing (b2a_profile_enable / b2a_profile_read).  The launchers
+// call profile_mark(kind, false, stream) right before and profile_mark(kind, true, stream)
+// right after the main kernel launch; both are no-ops unless profiling is enabled.
+void profile_mark(int kernel, bool after, cudaStream_t stream);
+
 }  // namespace b2a
