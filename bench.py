@@ -73,12 +73,13 @@ class ClockSampler:
         self.samples = []
         self.proc = None
         self.thread = None
+        self.window = [None, None]   # sample-count marks bracketing the timed region
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -92,6 +93,12 @@ class ClockSampler:
             if len(parts) >= 6:
                 self.samples.append(parts)
 
+    def mark_begin(self):
+        self.window[0] = len(self.samples)
+
+    def mark_end(self):
+        self.window[1] = len(self.samples)
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -104,7 +111,11 @@ class ClockSampler:
             self.thread.join(timeout=2)
         sm, sm_max, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for parts in self.samples:
+        lo = self.window[0] or 0
+        hi = self.window[1] if self.window[1] is not None else len(self.samples)
+        # keep one sample either side so that short timed regions still see a reading
+        chosen = self.samples[max(lo - 1, 0):hi + 1]
+        for parts in chosen:
             try:
                 sm.append(float(parts[0]))
                 sm_max.append(float(parts[1]))
@@ -238,19 +249,21 @@ def run_cuda_arm(args) -> None:
     flops = fwd_flops + bwd_flops
 
     # ---- device-resident timing -------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step_resident()
     barrier()
     lib.b2a_profile_enable(1)
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark_begin()
     e0.record()
     for _ in range(args.steps):
         step_resident()
     e1.record()
     barrier()
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     ms_total = e0.elapsed_time(e1)
     buf = (ctypes.c_float * 256)()
@@ -278,18 +291,20 @@ def run_cuda_arm(args) -> None:
         out_host["v"].copy_(dv, non_blocking=True)
 
     e2e_steps = max(2, min(args.steps, 5))
-    for _ in range(2):
-        step_e2e()
-    barrier()
-    e0.record()
-    for _ in range(e2e_steps):
-        step_e2e()
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = t.item() / e2e_steps
+    e2e_ms = None
+    if not args.skip_e2e:
+        for _ in range(2):
+            step_e2e()
+        barrier()
+        e0.record()
+        for _ in range(e2e_steps):
+            step_e2e()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item() / e2e_steps
     h2d = sum(host[n].numel() * 2 for n in ("q", "k", "v", "dout"))
     d2h = o_host.numel() * 2 + sum(out_host[n].numel() * 2 for n in ("q", "k", "v"))
 
@@ -323,13 +338,13 @@ def run_cuda_arm(args) -> None:
                      "unit": "TFLOP/s", "frac": achieved / (sustained or burst) if achieved else None,
                      "frac_of_burst": achieved / burst if achieved else None,
                      "traffic": None},
-        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12 if e2e_ms else None, "unit": UNIT,
+                "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": 4 * args.steps,
         "gpu_launches_note": "per step: fwd_kernel, bwd_preprocess_kernel, bwd_kernel, bwd_postprocess_kernel",
         "clocks": clocks,
     }
-    if world == 1:
+    if world == 1 and not args.skip_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_record(args.cpu_seconds)
     traffic_file = ROOT / "profiles" / "bwd_kernel_traffic.json"
     if traffic_file.exists():
@@ -342,12 +357,19 @@ def run_cuda_arm(args) -> None:
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=30)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("cuda", "reference"), default="cuda")
     parser.add_argument("--cpu-seconds", type=float, default=15.0,
                         help="time budget of the CPU baseline sample (N=1 only)")
+    parser.add_argument("--batch", type=int, default=None,
+                        help="override the per-GPU batch (smaller cases for profiler captures)")
+    parser.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
+    parser.add_argument("--skip-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
     args = parser.parse_args()
+    if args.batch is not None:
+        WORKLOAD["batch"] = args.batch
+        WORKLOAD["name"] = WORKLOAD["name"].replace("_B4_", f"_B{args.batch}_")
     if args.impl == "reference":
         run_reference_arm(args)
     else:
