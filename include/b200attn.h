@@ -78,6 +78,34 @@ size_t b2a_fwd_workspace_bytes(int32_t batch, int32_t total_q, int32_t is_varlen
  */
 int b2a_fwd(const b2a_fwd_args* args, void* cuda_stream);
 
+/*
+ * Forward for callers that must not allocate device memory.  No counterpart in the
+ * reference (its bindings allocate outputs and scratch on every call, bindings.cpp:267-269).
+ *
+ * Who needs it: code that runs where cudaMalloc is unavailable or forbidden -- a plugin
+ * inside a serving runtime that hands out one fixed memory pool at start-up, a hard
+ * real-time loop that may not touch the allocator, or a call site that owns q/k/v/out/lse
+ * but has no way to size and pass a workspace.  Same computation and arguments as b2a_fwd,
+ * except that args->workspace / workspace_bytes are ignored: the scratch (scheduler ticket,
+ * status word and the varlen work list) lives in a 64 KiB array built into the library,
+ * resident on every GPU that loads it.  The call and everything under it use no cudaMalloc,
+ * cudaFree or allocating library routine.
+ *
+ * Limit: problems whose scratch exceeds b2a_fwd_noalloc_scratch_limit() bytes -- packed
+ * batches with total_q / 256 + batch + 1 > 8190; fixed-length BSHD always fits -- are
+ * rejected with B2A_ERR_WORKSPACE_TOO_SMALL and a message naming both sizes.
+ * Set-up: the first call on each device (with that device current) looks up the array's
+ * device address; make that first call before starting any stream capture.
+ * Sharing: all calls on a device use the same array.  The words that must start at zero are
+ * cleared on the stream by every call; the rest keeps the previous call's contents.  Two
+ * calls that may overlap on the GPU (different streams, no dependency) race on it -- order
+ * them, or use b2a_fwd with separate workspaces.
+ */
+int b2a_fwd_noalloc(const b2a_fwd_args* args, void* cuda_stream);
+
+/* Size in bytes of the built-in scratch of b2a_fwd_noalloc. */
+size_t b2a_fwd_noalloc_scratch_limit(void);
+
 /* ------------------------------------------------------------------------- */
 /* Backward                                                                   */
 /* ------------------------------------------------------------------------- */

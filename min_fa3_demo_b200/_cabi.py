@@ -87,6 +87,8 @@ SIGNATURES = {
     "b2a_last_error": (c_char_p, []),
     "b2a_fwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32]),
     "b2a_fwd": (c_int32, [POINTER(FwdArgs), c_void_p]),
+    "b2a_fwd_noalloc": (c_int32, [POINTER(FwdArgs), c_void_p]),
+    "b2a_fwd_noalloc_scratch_limit": (c_size_t, []),
     "b2a_bwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b2a_bwd": (c_int32, [POINTER(BwdArgs), c_void_p]),
     "b2a_check_status": (c_int32, [c_void_p, c_void_p]),

@@ -3,6 +3,7 @@
 #include "b2a_host.cuh"
 
 #include <cmath>
+#include <mutex>
 
 namespace b2a {
 
@@ -142,6 +143,75 @@ int b2a_fwd(const b2a_fwd_args* a, void* cuda_stream) {
     profile_mark(B2A_KERNEL_FWD, true, stream);
     B2A_CUDA_OK(cudaGetLastError());
     return B2A_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Forward for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------
+namespace b2a {
+namespace {
+
+// Scratch of b2a_fwd_noalloc: the 16-byte workspace header plus the varlen work list.
+// 64 KiB holds 8190 work pieces (a piece is 256 query rows of one document), i.e. packed
+// batches with total_q / 256 + batch + 1 <= 8190.  Every GPU that loads the library keeps
+// this array resident until the process exits.
+constexpr size_t kNoAllocScratchBytes = 64 * 1024;
+static __device__ __align__(256) unsigned char g_fwd_noalloc_scratch[kNoAllocScratchBytes];
+
+// Device address of the array on each device.  The array's name is only a host-side handle
+// in host code; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
+// device while that device is current.
+int noalloc_scratch_ptr(void** out) {
+    static std::mutex mu;
+    static void* ptrs[64] = {};
+    int dev = 0;
+    B2A_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        return fail(B2A_ERR_CUDA, "device index %d out of range", dev);
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&p, g_fwd_noalloc_scratch);
+        if (err != cudaSuccess || p == nullptr) {
+            return fail(B2A_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed on device %d: %s", dev,
+                        cudaGetErrorString(err));
+        }
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return B2A_OK;
+}
+
+}  // namespace
+}  // namespace b2a
+
+extern "C" {
+
+size_t b2a_fwd_noalloc_scratch_limit(void) { return b2a::kNoAllocScratchBytes; }
+
+int b2a_fwd_noalloc(const b2a_fwd_args* a, void* cuda_stream) {
+    using namespace b2a;
+    B2A_REQUIRE(a != nullptr, "args must not be NULL");
+    B2A_REQUIRE(a->batch >= 1 && a->total_q >= 1, "batch and total_q must be positive");
+    const bool varlen = a->cu_seqlens_q != nullptr;
+    const size_t need = b2a_fwd_workspace_bytes(a->batch, a->total_q, varlen ? 1 : 0);
+    if (need > kNoAllocScratchBytes) {
+        return fail(B2A_ERR_WORKSPACE_TOO_SMALL,
+                    "b2a_fwd_noalloc: this problem needs %zu bytes of scratch but the built-in scratch "
+                    "holds %zu (packed batches up to total_q / 256 + batch + 1 <= 8190); "
+                    "use b2a_fwd with a caller-provided workspace",
+                    need, kNoAllocScratchBytes);
+    }
+    void* scratch = nullptr;
+    int rc = noalloc_scratch_ptr(&scratch);
+    if (rc != B2A_OK) return rc;
+    b2a_fwd_args local = *a;
+    local.workspace = scratch;
+    local.workspace_bytes = kNoAllocScratchBytes;
+    return b2a_fwd(&local, cuda_stream);
 }
 
 }  // extern "C"
