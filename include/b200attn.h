@@ -151,6 +151,84 @@ size_t b2a_bwd_workspace_bytes(int32_t batch, int32_t total_q, int32_t total_k, 
 int b2a_bwd(const b2a_bwd_args* args, void* cuda_stream);
 
 /* ------------------------------------------------------------------------- */
+/* Peer memory (single node, NVLink)                                          */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Export a device buffer for other processes of the node: writes the 64-byte CUDA-IPC
+ * handle of the allocation that contains `ptr` and the byte offset of `ptr` inside it.
+ * Together with b2a_ipc_import this replaces the peer-pointer table of the reference's
+ * TKParallelTensor (`raw_ptrs_`, csrc/backward/min_fa3_bwd_bindings.cu:711-715; created at
+ * min_fa3_op.py:201-206).  Carrying the offset explicitly avoids mapping an offset view at
+ * its allocation base (problem_record/tkparallel_ipc_offset_repro/README.md:15-27).
+ */
+int b2a_ipc_export(const void* ptr, unsigned char* handle64, uint64_t* offset);
+
+/* Map a buffer exported by another process; *out_ptr is usable by kernels on this device. */
+int b2a_ipc_import(const unsigned char* handle64, uint64_t offset, void** out_ptr);
+
+/* Unmap a pointer returned by b2a_ipc_import (pass the same offset). */
+int b2a_ipc_close(void* ptr, uint64_t offset);
+
+/*
+ * Copy `bytes` (multiple of 16) from `src` (typically a peer pointer) to local `dst` with
+ * `num_blocks` CTAs of bulk asynchronous copies through shared memory.  Replaces
+ * RemoteLoadTileKernel / RemoteLoadVecKernel (csrc/parallel/remote_load.cu:21-128).
+ * `status` may be NULL or point to a zeroed device word that receives an error code if a
+ * bounded wait runs out.
+ */
+int b2a_peer_copy(void* dst, const void* src, size_t bytes, int32_t num_blocks,
+                  unsigned int* status, void* cuda_stream);
+
+/* ------------------------------------------------------------------------- */
+/* Context-parallel forward ("mega ring")                                     */
+/* ------------------------------------------------------------------------- */
+
+typedef struct b2a_ring_fwd_args {
+    const void* q;                       /* bf16 [total_q, heads_q, 128], this rank's queries */
+    void* out;                           /* bf16 [total_q, heads_q, 128] */
+    float* lse;                          /* fp32 [heads_q, total_q] */
+    void* arena_k;                       /* bf16 [world_size * rank_kv_capacity, heads_k, 128]: rank-major */
+    void* arena_v;                       /*   K/V arena of this rank; rank r's keys live in rows [r*cap, ...) */
+    const void* peer_k[8];               /* arena_k base of every rank as mapped on this device */
+    const void* peer_v[8];
+    const int32_t* cu_seqlens_q_host;    /* HOST int32 [batch + 1]: this rank's local document offsets */
+    const int32_t* global_seqlens_host;  /* HOST int32 [batch]: document length over its whole ring */
+    const int32_t* ring_sizes_host;      /* HOST int32 [batch]: 1, 2, 4 or 8, non-increasing */
+    const int32_t* ring_starts_host;     /* HOST int32 [batch]: first rank of the ring, multiple of its size */
+    int64_t* stats;                      /* optional device int64[2]: (query-tile visits, K/V tile reads) */
+    int32_t batch;
+    int32_t world_size;
+    int32_t rank;
+    int32_t rank_kv_capacity;            /* arena rows per rank, multiple of 128 */
+    int32_t total_q;
+    int32_t heads_q;
+    int32_t heads_k;
+    int32_t head_dim;
+    int32_t is_causal;                   /* zigzag causal: rank r of a ring of G holds half-chunks r and 2G-1-r */
+    int32_t num_comp_sm;                 /* CTAs that only compute */
+    int32_t num_comm_sm;                 /* CTAs that first copy peers' K/V into the arena, then compute */
+    void* workspace;
+    size_t workspace_bytes;
+} b2a_ring_fwd_args;
+
+size_t b2a_ring_fwd_workspace_bytes(int32_t batch, int32_t world_size, int32_t rank_kv_capacity,
+                                    int32_t total_q);
+
+/*
+ * Context-parallel attention forward over a single node: every document is sharded over a
+ * ring of 1/2/4/8 ranks (zigzag halves when causal).  One launch per rank: copy CTAs pull the
+ * K/V blocks of the other ring members from their arenas over NVLink into this rank's arena
+ * and flag each 128-row block; compute CTAs run attention over local blocks first and over
+ * remote blocks as their flags appear, keeping the softmax state on chip across all ring
+ * members (no partial O/LSE round trips).  Every rank must have written its own arena slice
+ * and all ranks must have synchronised before the call.  Replaces
+ * `forward_varlen_mega_ring` (csrc/mega_ring_min_fa3_varlen_ring_bindings.cu:304) including
+ * the hierarchical sub-rings (include/min_fa3_mega_ring_hierarchy.h:13-33).
+ */
+int b2a_ring_fwd(const b2a_ring_fwd_args* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------- */
 /* Device status                                                              */
 /* ------------------------------------------------------------------------- */
 

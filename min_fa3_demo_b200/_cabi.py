@@ -81,6 +81,38 @@ class BwdArgs(Structure):
     ]
 
 
+class RingFwdArgs(Structure):
+    """Mirror of ``b2a_ring_fwd_args``."""
+
+    _fields_ = [
+        ("q", c_void_p),
+        ("out", c_void_p),
+        ("lse", c_void_p),
+        ("arena_k", c_void_p),
+        ("arena_v", c_void_p),
+        ("peer_k", c_void_p * 8),
+        ("peer_v", c_void_p * 8),
+        ("cu_seqlens_q_host", c_void_p),
+        ("global_seqlens_host", c_void_p),
+        ("ring_sizes_host", c_void_p),
+        ("ring_starts_host", c_void_p),
+        ("stats", c_void_p),
+        ("batch", c_int32),
+        ("world_size", c_int32),
+        ("rank", c_int32),
+        ("rank_kv_capacity", c_int32),
+        ("total_q", c_int32),
+        ("heads_q", c_int32),
+        ("heads_k", c_int32),
+        ("head_dim", c_int32),
+        ("is_causal", c_int32),
+        ("num_comp_sm", c_int32),
+        ("num_comm_sm", c_int32),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+    ]
+
+
 # symbol -> (restype, argtypes); must list every function include/b200attn.h declares.
 SIGNATURES = {
     "b2a_abi_version": (c_int32, []),
@@ -91,6 +123,12 @@ SIGNATURES = {
     "b2a_fwd_noalloc_scratch_limit": (c_size_t, []),
     "b2a_bwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b2a_bwd": (c_int32, [POINTER(BwdArgs), c_void_p]),
+    "b2a_ipc_export": (c_int32, [c_void_p, c_void_p, POINTER(ctypes.c_uint64)]),
+    "b2a_ipc_import": (c_int32, [c_void_p, ctypes.c_uint64, POINTER(c_void_p)]),
+    "b2a_ipc_close": (c_int32, [c_void_p, ctypes.c_uint64]),
+    "b2a_peer_copy": (c_int32, [c_void_p, c_void_p, c_size_t, c_int32, c_void_p, c_void_p]),
+    "b2a_ring_fwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32]),
+    "b2a_ring_fwd": (c_int32, [POINTER(RingFwdArgs), c_void_p]),
     "b2a_check_status": (c_int32, [c_void_p, c_void_p]),
     "b2a_profile_enable": (c_int32, [c_int32]),
     "b2a_profile_read": (c_int32, [c_int32, POINTER(c_float), c_int32]),

@@ -65,6 +65,28 @@ struct FwdParams {
     // is visible to local query row r when c + k_pos_offset <= r + q_pos_offset + (k_len - q_len)
     // (both 0 for plain attention).
     uint32_t timeout_ns;
+    // ---- context-parallel ("mega ring") mode: all of this is null / 0 otherwise -------
+    const struct RingDoc* ring_docs;   // per document ring placement (device)
+    const int4* ring_work;             // (doc, half, row-pair index, 0) in LPT order
+    const int2* comm_tasks;            // (source rank, arena 128-row block) in fetch order
+    int comm_task_count;
+    int num_comp;                      // CTAs [num_comp, gridDim.x) start as copy CTAs
+    int my_rank;
+    int kv_row_bytes;                  // heads_k * 256
+    const uint8_t* peer_k[8];          // arena base of every rank as mapped on this device
+    const uint8_t* peer_v[8];
+    uint8_t* arena_k;                  // this rank's arena (the tensor maps of K/V cover it)
+    uint8_t* arena_v;
+    int* kv_flags;                     // per 128-row arena block: 1 once K and V have landed
+};
+
+// Placement of one document on its ring.  Lengths are in tokens, multiples of 128.
+struct RingDoc {
+    int q_begin;        // first local token of the document on this rank
+    int half_len;       // local length / 2 for rings, local length for ring_size 1
+    int ring_size;      // G
+    int ring_rank;      // this rank's position in the ring (global rank - ring_start)
+    int member_row[8];  // arena row of the document's slice on ring member s
 };
 
 struct FwdWork {
@@ -76,6 +98,9 @@ struct FwdWork {
     int head;
     int head_k;
     long long lse_base;   // element offset of document row 0 for this head
+    int n_full;    // ring mode: unmasked K/V blocks of other chunks that precede the own chunk
+    int doc;       // ring mode: document index
+    int half;      // ring mode: 0 = front half, 1 = back half of the local zigzag shard
 };
 
 struct __align__(1024) FwdShared {
@@ -90,16 +115,46 @@ struct __align__(1024) FwdShared {
     uint64_t o_full[kFwdTilesPerCta];
     uint64_t sched_full[2];
     uint64_t sched_empty[2];
+    uint64_t comm_full[6];
+    uint64_t comm_empty[6];
     int sched_w[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
+
+// Number of whole (unmasked) chunks a query half sees before its own chunk.  A chunk is
+// half_len tokens: zigzag rank r of a ring of G holds global chunks r (front) and 2G-1-r
+// (back); causally a query chunk sees every chunk with a smaller global index.
+__device__ __forceinline__ int ring_full_chunks(int causal, int ring_size, int ring_rank, int half) {
+    if (causal) {
+        if (ring_size == 1) return 0;
+        return half == 0 ? ring_rank : 2 * ring_size - 1 - ring_rank;
+    }
+    return ring_size == 1 ? 1 : 2 * ring_size;
+}
 
 __device__ __forceinline__ FwdWork fwd_decode_work(const FwdParams& p, int w) {
     FwdWork wk;
     int entry = w / p.heads_q;
     wk.head = w - entry * p.heads_q;
     wk.head_k = wk.head / (p.heads_q / p.heads_k);
+    wk.n_full = 0;
+    wk.doc = 0;
+    wk.half = 0;
+    if (p.ring_docs != nullptr) {
+        const int4 e = p.ring_work[entry];
+        const RingDoc& d = p.ring_docs[e.x];
+        wk.doc = e.x;
+        wk.half = e.y;
+        wk.q_begin = d.q_begin + e.y * d.half_len;
+        wk.q_len = d.half_len;
+        wk.k_begin = 0;
+        wk.k_len = p.causal ? d.half_len : 0;   // own-chunk keys (none when everything is unmasked)
+        wk.m0 = e.z * kFwdRowsPerWork;
+        wk.n_full = ring_full_chunks(p.causal, d.ring_size, d.ring_rank, e.y) * (d.half_len / kTileN);
+        wk.lse_base = static_cast<long long>(wk.head) * p.lse_head_stride + wk.q_begin;
+        return wk;
+    }
     if (p.cu_seqlens_q == nullptr) {
         int nmb = (p.seqlen_q + kFwdRowsPerWork - 1) / kFwdRowsPerWork;
         int b = entry / nmb;
@@ -137,10 +192,137 @@ __device__ __forceinline__ int fwd_num_kv_blocks(const FwdParams& p, const FwdWo
         int row_last = min(row0 + kTileM, wk.q_len) - 1;
         limit = min(limit, row_last + 1 + wk.k_len - wk.q_len);
     }
-    if (limit <= 0) {
-        return 0;
+    const int own = limit <= 0 ? 0 : (limit + kTileN - 1) / kTileN;
+    return wk.n_full + own;
+}
+
+// Ring mode: arena row of virtual K/V block j of a work item, and whether it comes from
+// another rank (then its arena block must be flagged ready before it is read).  Blocks
+// j >= n_full are the own (diagonal) chunk; below that the chunks are visited in the order
+// the copy CTAs fetch them: the other local half, then sources r-1, r-2, ... around the ring.
+__device__ __forceinline__ int ring_kv_row(const FwdParams& p, const FwdWork& wk, int j, bool* remote) {
+    const RingDoc& d = p.ring_docs[wk.doc];
+    const int hb = d.half_len / kTileN;
+    const int g = d.ring_size;
+    const int r = d.ring_rank;
+    int s, hf, blk;
+    if (j >= wk.n_full) {
+        s = r;
+        hf = wk.half;
+        blk = j - wk.n_full;
+    } else {
+        const int idx = wk.n_full - 1 - j;
+        const int slot = idx / hb;
+        blk = idx - slot * hb;
+        if (p.causal) {
+            if (wk.half == 0) {
+                s = r - 1 - slot;
+                hf = 0;
+            } else if (slot <= r) {
+                s = r - slot;
+                hf = 0;
+            } else {
+                const int k = slot - r - 1;
+                s = g - 1 - (k >> 1);
+                hf = k & 1;
+            }
+        } else if (g == 1) {
+            s = 0;
+            hf = 0;
+        } else if (slot < 2) {
+            s = r;
+            hf = slot;
+        } else {
+            const int k = slot - 2;
+            s = (r - 1 - (k >> 1) + g) % g;
+            hf = k & 1;
+        }
     }
-    return (limit + kTileN - 1) / kTileN;
+    *remote = (s != r);
+    return d.member_row[s] + hf * d.half_len + blk * kTileN;
+}
+
+// Bounded wait until a device-scope flag word becomes non-zero (acquire).
+__device__ __forceinline__ bool flag_wait(const WaitCtx& ctx, const int* flag, uint32_t tag) {
+    const uint32_t start = global_timer_lo();
+    uint32_t polls = 0;
+#pragma unroll 1
+    while (true) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v != 0) return true;
+        if ((++polls & 0xFu) == 0u) {
+            if (ld_shared_volatile_u32(ctx.abort_smem) != 0u) return false;
+            if (global_timer_lo() - start > ctx.timeout_ns) {
+                st_shared_volatile_u32(ctx.abort_smem, 1u);
+                set_status(ctx.status, kStatusTimeout, (tag << 12) | (blockIdx.x & 0xFFFu));
+                return false;
+            }
+            __nanosleep(100);
+        }
+    }
+}
+
+// Copy role of a ring-mode CTA: tasks are 128-row arena blocks owned by other ranks.  One
+// thread streams 32 KiB bulk loads peer -> shared (6 slots over the Q and K/V tile buffers),
+// another streams bulk stores shared -> local arena and publishes the block's flag once its
+// K and V have both landed.  No multicast; every wait is bounded.
+__device__ __forceinline__ void ring_copy_role(const FwdParams& p, FwdShared& sh, const WaitCtx& wctx,
+                                               int warp, int lane) {
+    constexpr uint32_t kSlotBytes = kTileBytes;   // 32 KiB
+    const uint32_t block_bytes = static_cast<uint32_t>(kTileN) * p.kv_row_bytes;
+    const uint32_t chunks = block_bytes / kSlotBytes;
+    const uint32_t slot_base = smem_u32(&sh.q[0][0]);
+    const int first = static_cast<int>(blockIdx.x) - p.num_comp;
+    const int stride = static_cast<int>(gridDim.x) - p.num_comp;
+    if (warp == 9 && lane == 0) {
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = first; t < p.comm_task_count && ok; t += stride) {
+            const int2 task = p.comm_tasks[t];
+            const size_t off = static_cast<size_t>(task.y) * block_bytes;
+            for (int kv = 0; kv < 2 && ok; ++kv) {
+                const uint8_t* src = (kv == 0 ? p.peer_k[task.x] : p.peer_v[task.x]) + off;
+                for (uint32_t c = 0; c < chunks; ++c, ++it) {
+                    const uint32_t slot = it % 6u;
+                    ok = mbar_wait(wctx, smem_u32(&sh.comm_empty[slot]), ((it / 6u) & 1u) ^ 1u, 14);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(smem_u32(&sh.comm_full[slot]), kSlotBytes);
+                    bulk_load_1d(slot_base + slot * kSlotBytes, src + static_cast<size_t>(c) * kSlotBytes,
+                                 kSlotBytes, smem_u32(&sh.comm_full[slot]));
+                }
+            }
+        }
+    } else if (warp == 10 && lane == 0) {
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = first; t < p.comm_task_count && ok; t += stride) {
+            const int2 task = p.comm_tasks[t];
+            const size_t off = static_cast<size_t>(task.y) * block_bytes;
+            for (int kv = 0; kv < 2 && ok; ++kv) {
+                uint8_t* dst = (kv == 0 ? p.arena_k : p.arena_v) + off;
+                for (uint32_t c = 0; c < chunks; ++c, ++it) {
+                    const uint32_t slot = it % 6u;
+                    ok = mbar_wait(wctx, smem_u32(&sh.comm_full[slot]), (it / 6u) & 1u, 15);
+                    if (!ok) break;
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 ::"l"(reinterpret_cast<uint64_t>(dst + static_cast<size_t>(c) * kSlotBytes)),
+                                   "r"(slot_base + slot * kSlotBytes), "r"(kSlotBytes)
+                                 : "memory");
+                    bulk_commit_group();
+                    bulk_wait_group_read<0>();
+                    mbar_arrive(smem_u32(&sh.comm_empty[slot]));
+                }
+            }
+            if (ok) {
+                bulk_wait_group<0>();        // the block's K and V are in the arena
+                fence_proxy_async_all();
+                asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.kv_flags + task.y), "r"(1)
+                             : "memory");
+            }
+        }
+        bulk_wait_group<0>();
+    }
 }
 
 template <bool kMerge>
@@ -170,6 +352,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             mbar_init(smem_u32(&sh.sched_full[i]), 1);
             mbar_init(smem_u32(&sh.sched_empty[i]), 1 + 2 * 4);  // MMA warp + 8 softmax warps
         }
+        for (int i = 0; i < 6; ++i) {
+            mbar_init(smem_u32(&sh.comm_full[i]), 1);
+            mbar_init(smem_u32(&sh.comm_empty[i]), 1);
+        }
         sh.abort_flag = 0;
         fence_mbar_init();
         fence_proxy_async_smem();
@@ -187,6 +373,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 
     const int total_work =
         (p.cu_seqlens_q == nullptr ? p.num_entries_host : *p.num_entries_dev) * p.heads_q;
+
+    // Copy CTAs (ring mode): pull the other ranks' K/V blocks into the local arena first, then
+    // join the attention work queue like every other CTA.
+    if (p.ring_docs != nullptr && static_cast<int>(blockIdx.x) >= p.num_comp && p.comm_task_count > 0) {
+        ring_copy_role(p, sh, wctx, warp, lane);
+        __syncthreads();
+    }
 
     if (warp >= 8) {
         reg_dealloc<72>();
@@ -242,11 +435,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                                        ((kv_it / kFwdStages) & 1u) ^ 1u, 3);
                         if (!ok) break;
                         ++kv_it;
+                        int row = wk.k_begin + j * kTileN;
+                        if (p.ring_docs != nullptr) {
+                            bool remote = false;
+                            row = ring_kv_row(p, wk, j, &remote);
+                            if (remote && kv == 0) {
+                                ok = flag_wait(wctx, p.kv_flags + row / kTileN, 13);
+                                if (!ok) break;
+                                fence_proxy_async_all();
+                            }
+                        }
                         if (lane == 0) {
                             const uint32_t bar = smem_u32(&sh.kv_full[stage]);
                             const uint32_t dst = smem_u32(&sh.kv[stage][0]);
                             const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
-                            const int row = wk.k_begin + j * kTileN;
                             mbar_arrive_expect_tx(bar, kTileBytes);
                             tma_load_3d(dst, map, bar, 0, wk.head_k, row);
                             tma_load_3d(dst + kHalfTileBytes, map, bar, 64, wk.head_k, row);
@@ -443,8 +645,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 }
                 tmem_wait_ld();
 
-                const int n0 = j * kTileN;
-                if (n0 + kTileN > tile_min_limit) {
+                const int n0 = (j - wk.n_full) * kTileN;   // own-chunk column of the block
+                if (j >= wk.n_full && n0 + kTileN > tile_min_limit) {
                     const int lim = col_limit - n0;
 #pragma unroll
                     for (int i = 0; i < kTileN; ++i) {

@@ -18,10 +18,16 @@ import torch
 from . import _cabi
 
 __all__ = [
+    "TKParallelTensor",
     "forward",
     "forward_varlen",
+    "forward_varlen_ring",
+    "forward_varlen_mega_ring",
     "backward",
     "backward_varlen",
+    "create_parallel_tensor",
+    "parallel_remote_load",
+    "parallel_remote_load_vec",
     "_debug_resolve_launch_grid_shape",
 ]
 
@@ -397,3 +403,10 @@ def backward_varlen(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: tor
               heads_q=q.size(1), heads_k=k.size(1), is_causal=is_causal,
               deterministic=deterministic)
     return dq, dk, dv
+
+
+# Context-parallel entry points and peer-memory helpers live in their own modules; they are
+# re-exported here so that this module carries the whole reference API surface.
+from .parallel import (TKParallelTensor, _resolve_parallel_context, create_parallel_tensor,  # noqa: E402,F401
+                       parallel_remote_load, parallel_remote_load_vec)
+from .ring import forward_varlen_mega_ring, forward_varlen_ring  # noqa: E402,F401

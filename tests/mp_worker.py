@@ -1,0 +1,266 @@
+"""Multi-rank worker for the context-parallel GPU tests.  Launched by tests/test_ring_gpu.py as
+``python -m torch.distributed.run --nproc-per-node W tests/mp_worker.py <case>`` (one rank per GPU)
+or run in-process with world size 1.  Every rank builds the same global problem from a seed,
+keeps its zigzag shard, runs the CUDA path and checks it against the CPU oracle; failures are
+voted across ranks so that every rank exits with the same status
+(reference: scripts/test_min_fa3/test_min_fa3_varlen_ring_multi_rank.py:46-53)."""
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+import min_fa3_op  # noqa: E402
+from oracle import attention_oracle as orc  # noqa: E402
+
+SENTINEL = -123.0
+BASE_SEED = 20260713
+
+
+def setup():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    return rank, world, torch.device("cuda", local_rank)
+
+
+def barrier(world):
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+
+
+def vote(ok: bool, world: int, what: str, rank: int) -> None:
+    flag = torch.tensor([0 if ok else 1], device="cuda", dtype=torch.int32)
+    if world > 1:
+        dist.all_reduce(flag)
+    if flag.item() != 0:
+        raise SystemExit(f"[rank {rank}] {what}: FAILED on {flag.item()} rank(s)")
+    if rank == 0:
+        print(f"{what}: ok", flush=True)
+
+
+def local_positions(g: int, r: int, local_len: int, causal: bool) -> torch.Tensor:
+    """Global token positions of ring member r's shard (zigzag halves for causal rings)."""
+    if g == 1:
+        return torch.arange(local_len)
+    if causal:
+        return orc.zigzag_positions(g, r, local_len)
+    return torch.arange(local_len) + r * local_len
+
+
+def build_problem(world: int, rank: int, docs, qh: int, kvh: int, causal: bool, seed: int):
+    """docs: list of (global_len, ring_size, ring_start), ring sizes non-increasing.
+    Returns this rank's packed q, k, v, dout (bf16 CPU), cu_seqlens and, per member document,
+    the global tensors for the oracle."""
+    gen = torch.Generator().manual_seed(seed)
+    q_parts, k_parts, v_parts, d_parts, lens, oracle_docs = [], [], [], [], [], []
+    for (glen, g, start) in docs:
+        qg = torch.randn(glen, qh, 128, generator=gen).to(torch.bfloat16)
+        kg = torch.randn(glen, kvh, 128, generator=gen).to(torch.bfloat16)
+        vg = (torch.randn(glen, kvh, 128, generator=gen) * 0.5).to(torch.bfloat16)
+        dg = torch.randn(glen, qh, 128, generator=gen).to(torch.bfloat16)
+        member = start <= rank < start + g
+        if not member:
+            lens.append(0)
+            continue
+        pos = local_positions(g, rank - start, glen // g, causal)
+        q_parts.append(qg[pos]); k_parts.append(kg[pos]); v_parts.append(vg[pos]); d_parts.append(dg[pos])
+        lens.append(glen // g)
+        oracle_docs.append((qg, kg, vg, dg, pos))
+    cu = torch.tensor([0, *torch.tensor(lens).cumsum(0).tolist()], dtype=torch.int32)
+
+    def cat(parts, heads):
+        return torch.cat(parts) if parts else torch.zeros(0, heads, 128, dtype=torch.bfloat16)
+    return cat(q_parts, qh), cat(k_parts, kvh), cat(v_parts, kvh), cat(d_parts, qh), cu, oracle_docs
+
+
+def oracle_forward(oracle_docs, causal):
+    outs, lses = [], []
+    for (qg, kg, vg, _dg, pos) in oracle_docs:
+        kpos = torch.arange(kg.size(0)) if causal else None
+        o, l = orc.attention_positions(qg[pos], kg, vg, pos if causal else None, kpos)
+        outs.append(o); lses.append(l)
+    return torch.cat(outs), torch.cat(lses, dim=1)
+
+
+def make_arena(world, rank, cap, local_k, local_v, dev):
+    """Rank-major K/V arenas as parallel tensors; only the owner slice is written, the rest keeps
+    a sentinel (reference: ...hybrid_multi_rank.py:159-189)."""
+    kvh = local_k.size(1)
+    ak = torch.full((world * cap, kvh, 128), SENTINEL, dtype=torch.bfloat16, device=dev)
+    av = torch.full((world * cap, kvh, 128), SENTINEL, dtype=torch.bfloat16, device=dev)
+    n = local_k.size(0)
+    ak[rank * cap: rank * cap + n] = local_k.to(dev)
+    av[rank * cap: rank * cap + n] = local_v.to(dev)
+    rk = min_fa3_op.TKParallelTensor(ak, local_rank=dev.index, local_world_size=world, multicast=False)
+    rv = min_fa3_op.TKParallelTensor(av, local_rank=dev.index, local_world_size=world, multicast=False)
+    return rk, rv
+
+
+def meta(docs):
+    g = torch.tensor([d[0] for d in docs], dtype=torch.int32)
+    s = torch.tensor([d[1] for d in docs], dtype=torch.int32)
+    st = torch.tensor([d[2] for d in docs], dtype=torch.int32)
+    return g, s, st
+
+
+def ring_docs_for(world: int):
+    """A hierarchical mix: all-rank documents, sub-rings, single-rank documents."""
+    docs = [(world * 512, world, 0), (world * 256, world, 0)]
+    if world >= 4:
+        docs += [(1024, world // 2, 0), (512, world // 2, world // 2)]
+    if world >= 2:
+        docs += [(512, 1, 0), (256, 1, world - 1), (128, 1, 1 % world)]
+    else:
+        docs += [(384, 1, 0)]
+    return docs
+
+
+def case_mega_ring_fwd(rank, world, dev):
+    from min_fa3_demo_b200.min_fa3_op import check_device_status
+    qh, kvh = 8, 2
+    sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    for causal in (True, False):
+        docs = ring_docs_for(world)
+        q, k, v, _d, cu, odocs = build_problem(world, rank, docs, qh, kvh, causal, BASE_SEED + causal)
+        cap = 2048
+        rk, rv = make_arena(world, rank, cap, k, v, dev)
+        barrier(world)
+        g, s, st = meta(docs)
+        lens = (cu[1:] - cu[:-1]).tolist()
+        out = torch.full((q.size(0), qh, 128), SENTINEL, dtype=torch.bfloat16, device=dev)
+        lse = torch.full((qh, q.size(0)), SENTINEL, dtype=torch.float32, device=dev)
+        stats = torch.zeros(2, dtype=torch.int64, device=dev)
+        ok = True
+        for rep in range(3):   # repeated launches: flags and tickets must reset correctly
+            min_fa3_op.forward_varlen_mega_ring(
+                q.to(dev), rk.data_, rv.data_, cu.to(dev), cu.to(dev), max(max(lens), 1), max(max(lens), 1), causal,
+                cu_seqlens_q_host=cu, cu_seqlens_k_host=cu, remote_k=rk, remote_v=rv,
+                num_comp_sm=sm - 8, num_comm_sm=8, global_seqlens_host=g, ring_sizes_host=s,
+                ring_starts_host=st, out=out, lse=lse, return_lse=True, stats=stats)
+            torch.cuda.synchronize()
+            try:
+                check_device_status(min_fa3_op.forward_varlen_mega_ring.last_workspace)
+            except RuntimeError as exc:
+                print(f"[rank {rank}] device status: {exc}", flush=True)
+                ok = False
+            if q.size(0) > 0:
+                ref_o, ref_l = oracle_forward(odocs, causal)
+                eo = (out.float().cpu() - ref_o).abs().max().item()
+                el = (lse.cpu() - ref_l).abs().max().item()
+                if not (eo <= 1.6e-2 and el <= 1e-3):
+                    print(f"[rank {rank}] causal={causal} rep={rep}: O err {eo:.3e} LSE err {el:.3e}", flush=True)
+                    ok = False
+            barrier(world)
+        # arena rows never addressed by any ring keep their sentinel
+        tail = rk.data_[rank * cap + k.size(0): (rank + 1) * cap]
+        ok = ok and bool((tail.float() == SENTINEL).all().item())
+        ok = ok and stats[0].item() > 0 if q.size(0) > 0 else ok
+        vote(ok, world, f"mega_ring_fwd causal={causal} world={world}", rank)
+        barrier(world)
+
+
+def case_remote_load(rank, world, dev):
+    # bit-exact peer copy (reference: scripts/test_min_fa3/test_parallel_remote_load.py:77-90)
+    torch.manual_seed(100 + rank)
+    t = torch.randn(512, 1024, device=dev).to(torch.bfloat16)
+    pt = min_fa3_op.create_parallel_tensor(t, local_rank=dev.index, local_world_size=world)
+    vec = torch.randn(64, 4096, device=dev).to(torch.bfloat16)
+    pv = min_fa3_op.create_parallel_tensor(vec, local_rank=dev.index, local_world_size=world)
+    barrier(world)
+    ok = True
+    for src in range(world):
+        got = min_fa3_op.parallel_remote_load(pt, src, num_blocks=16)
+        gotv = min_fa3_op.parallel_remote_load_vec(pv, src, output=torch.empty_like(vec))
+        expect, expectv = t.clone(), vec.clone()
+        if world > 1:
+            dist.broadcast(expect, src)
+            dist.broadcast(expectv, src)
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(got, expect) and torch.equal(gotv, expectv)
+    try:
+        min_fa3_op.parallel_remote_load(pv, 0)
+        ok = False
+    except RuntimeError as exc:
+        ok = ok and "currently supports 2D" not in str(exc)
+    vote(ok, world, f"parallel_remote_load world={world}", rank)
+    barrier(world)
+
+
+def case_ring_steps(rank, world, dev):
+    """Plain (non-zigzag) ring built from forward_varlen_ring steps, as the reference's
+    benchmark loop does (ring_test/homogeneous_all_cp_microbench/benchmark_ring_forward.py:446-482)."""
+    qh, kvh, local = 4, 2, 384
+    sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    for causal in (False, True):
+        gen = torch.Generator().manual_seed(7 + causal)
+        qg = torch.randn(world * local, qh, 128, generator=gen).to(torch.bfloat16)
+        kg = torch.randn(world * local, kvh, 128, generator=gen).to(torch.bfloat16)
+        vg = torch.randn(world * local, kvh, 128, generator=gen).to(torch.bfloat16)
+        sl = slice(rank * local, (rank + 1) * local)
+        q, k, v = qg[sl].to(dev), kg[sl].to(dev), vg[sl].to(dev)
+        rk = min_fa3_op.create_parallel_tensor(k, local_rank=dev.index, local_world_size=world)
+        rv = min_fa3_op.create_parallel_tensor(v, local_rank=dev.index, local_world_size=world)
+        cu = torch.tensor([0, 128, local], dtype=torch.int32)
+        barrier(world)
+        pk = [torch.empty_like(k), torch.empty_like(k)]
+        pvv = [torch.empty_like(v), torch.empty_like(v)]
+        cur_k, cur_v, out, lse = k, v, None, None
+        for step in range(world):
+            if causal and step > rank:
+                break
+            nxt = (rank - step - 1 + world) % world
+            comm = 4 if step + 1 < world else 0
+            out, lse = min_fa3_op.forward_varlen_ring(
+                q, cur_k, cur_v, cu.to(dev), cu.to(dev), 256, 256, causal and step == 0,
+                cu_seqlens_q_host=cu, cu_seqlens_k_host=cu, remote_k=rk, remote_v=rv, src_rank=nxt,
+                num_comp_sm=sm - 4, num_comm_sm=comm, ring_step=step, prefetch_k=pk[step % 2],
+                prefetch_v=pvv[step % 2], out=out, lse=lse, return_lse=True)
+            if step + 1 < world:
+                cur_k, cur_v = pk[step % 2], pvv[step % 2]
+        torch.cuda.synchronize()
+        # two documents per rank: document j of every rank forms one global sequence in rank order
+        outs, lses = [], []
+        for (a, b) in ((0, 128), (128, local)):
+            n = b - a
+            kk = torch.cat([kg[r * local + a: r * local + b] for r in range(world)])
+            vv = torch.cat([vg[r * local + a: r * local + b] for r in range(world)])
+            qpos = torch.arange(n) + rank * n if causal else None
+            kpos = torch.arange(world * n) if causal else None
+            o, l = orc.attention_positions(qg[rank * local + a: rank * local + b], kk, vv, qpos, kpos)
+            outs.append(o); lses.append(l)
+        eo = (out.float().cpu() - torch.cat(outs)).abs().max().item()
+        el = (lse.cpu() - torch.cat(lses, dim=1)).abs().max().item()
+        # the running output is kept in bf16 between steps (as in the reference): one extra rounding per step
+        ok = eo <= 1.6e-2 + 4e-3 * world and el <= 1e-3
+        if not ok:
+            print(f"[rank {rank}] ring steps causal={causal}: O err {eo:.3e} LSE err {el:.3e}", flush=True)
+        vote(ok, world, f"forward_varlen_ring steps causal={causal} world={world}", rank)
+        barrier(world)
+
+
+CASES = {"mega_ring_fwd": case_mega_ring_fwd, "remote_load": case_remote_load, "ring_steps": case_ring_steps}
+
+
+def main(argv):
+    rank, world, dev = setup()
+    names = argv[1:] or list(CASES)
+    for name in names:
+        CASES[name](rank, world, dev)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main(sys.argv)
