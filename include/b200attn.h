@@ -228,6 +228,56 @@ size_t b2a_ring_fwd_workspace_bytes(int32_t batch, int32_t world_size, int32_t r
  */
 int b2a_ring_fwd(const b2a_ring_fwd_args* args, void* cuda_stream);
 
+typedef struct b2a_ring_bwd_args {
+    const void* dout;                    /* bf16 [total_q, heads_q, 128] */
+    const void* q;
+    const void* out;
+    const float* lse;                    /* fp32 [heads_q, total_q] from the forward */
+    void* dq;                            /* bf16 [total_q, heads_q, 128] */
+    void* dk;                            /* bf16 [local_total_k, heads_k, 128] (compact, not arena shaped) */
+    void* dv;
+    void* arena_k;                       /* as in b2a_ring_fwd_args */
+    void* arena_v;
+    const void* peer_k[8];
+    const void* peer_v[8];
+    float* dk_accum_peer[8];             /* fp32 dK accumulator of every rank, zeroed by the caller: */
+    float* dv_accum_peer[8];             /*   >= rank_kv_capacity * heads_k * 128 floats each */
+    int32_t* completion_peer[8];         /* int32[1] completion counter of every rank, zeroed by the caller */
+    const int32_t* cu_seqlens_q_host;
+    const int32_t* global_seqlens_host;
+    const int32_t* ring_sizes_host;
+    const int32_t* ring_starts_host;
+    int32_t batch;
+    int32_t world_size;
+    int32_t rank;
+    int32_t rank_kv_capacity;
+    int32_t total_q;
+    int32_t local_total_k;
+    int32_t heads_q;
+    int32_t heads_k;
+    int32_t head_dim;
+    int32_t is_causal;
+    int32_t num_comp_sm;
+    int32_t num_comm_sm;
+    void* workspace;
+    size_t workspace_bytes;
+} b2a_ring_bwd_args;
+
+size_t b2a_ring_bwd_workspace_bytes(int32_t batch, int32_t world_size, int32_t rank_kv_capacity,
+                                    int32_t total_q, int32_t heads_q);
+
+/*
+ * Context-parallel attention backward.  Each rank runs the KV-stationary backward over every
+ * key block (local or pulled from a ring member into the arena) that its queries see; dQ stays
+ * local, while the dK / dV partial tiles are added in fp32 straight into the accumulator of the
+ * rank that owns the key block (over NVLink for remote owners).  When a rank has added all its
+ * contributions it bumps every rank's completion counter; each rank waits (bounded) for its
+ * counter to reach the world size and then casts its accumulator to bf16 dk / dv.  The caller
+ * zeroes the accumulators and counters and synchronises all ranks before every call.  Replaces
+ * `backward_varlen_mega_ring` (csrc/backward/min_fa3_bwd_bindings.cu:375-722).
+ */
+int b2a_ring_bwd(const b2a_ring_bwd_args* args, void* cuda_stream);
+
 /* ------------------------------------------------------------------------- */
 /* Device status                                                              */
 /* ------------------------------------------------------------------------- */

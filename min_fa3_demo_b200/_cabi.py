@@ -113,6 +113,45 @@ class RingFwdArgs(Structure):
     ]
 
 
+class RingBwdArgs(Structure):
+    """Mirror of ``b2a_ring_bwd_args``."""
+
+    _fields_ = [
+        ("dout", c_void_p),
+        ("q", c_void_p),
+        ("out", c_void_p),
+        ("lse", c_void_p),
+        ("dq", c_void_p),
+        ("dk", c_void_p),
+        ("dv", c_void_p),
+        ("arena_k", c_void_p),
+        ("arena_v", c_void_p),
+        ("peer_k", c_void_p * 8),
+        ("peer_v", c_void_p * 8),
+        ("dk_accum_peer", c_void_p * 8),
+        ("dv_accum_peer", c_void_p * 8),
+        ("completion_peer", c_void_p * 8),
+        ("cu_seqlens_q_host", c_void_p),
+        ("global_seqlens_host", c_void_p),
+        ("ring_sizes_host", c_void_p),
+        ("ring_starts_host", c_void_p),
+        ("batch", c_int32),
+        ("world_size", c_int32),
+        ("rank", c_int32),
+        ("rank_kv_capacity", c_int32),
+        ("total_q", c_int32),
+        ("local_total_k", c_int32),
+        ("heads_q", c_int32),
+        ("heads_k", c_int32),
+        ("head_dim", c_int32),
+        ("is_causal", c_int32),
+        ("num_comp_sm", c_int32),
+        ("num_comm_sm", c_int32),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+    ]
+
+
 # symbol -> (restype, argtypes); must list every function include/b200attn.h declares.
 SIGNATURES = {
     "b2a_abi_version": (c_int32, []),
@@ -129,6 +168,8 @@ SIGNATURES = {
     "b2a_peer_copy": (c_int32, [c_void_p, c_void_p, c_size_t, c_int32, c_void_p, c_void_p]),
     "b2a_ring_fwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32]),
     "b2a_ring_fwd": (c_int32, [POINTER(RingFwdArgs), c_void_p]),
+    "b2a_ring_bwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),
+    "b2a_ring_bwd": (c_int32, [POINTER(RingBwdArgs), c_void_p]),
     "b2a_check_status": (c_int32, [c_void_p, c_void_p]),
     "b2a_profile_enable": (c_int32, [c_int32]),
     "b2a_profile_read": (c_int32, [c_int32, POINTER(c_float), c_int32]),

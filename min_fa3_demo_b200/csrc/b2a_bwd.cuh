@@ -58,6 +58,26 @@ struct BwdParams {
     float scale;
     float scale_log2;
     uint32_t timeout_ns;
+    // ---- context-parallel mode: null / 0 otherwise ------------------------------------
+    const RingDoc* ring_docs;
+    const int4* ring_work;             // (doc, source ring member, key half, 128-row block)
+    const int2* comm_tasks;            // (source rank, arena block) for the copy CTAs
+    int comm_task_count;
+    int num_comp;
+    int my_rank;
+    int ring_start_unused;
+    int kv_row_bytes;
+    int cap;                           // arena rows per rank
+    const uint8_t* peer_k[8];
+    const uint8_t* peer_v[8];
+    uint8_t* arena_k;
+    uint8_t* arena_v;
+    int* kv_flags;
+    float* dk_accum_peer[8];           // fp32 dK / dV accumulators of every rank (owner-directed adds)
+    float* dv_accum_peer[8];
+    int* completion_peer[8];           // completion counter of every rank
+    int* done_ctas;                    // local counter of finished CTAs
+    int world;
 };
 
 struct BwdWork {
@@ -68,9 +88,32 @@ struct BwdWork {
     int q_pad_begin;   // first padded row of the document (multiple of 128)
     int n0;            // first key row (document-local) of the block
     int head_k;
-    int m_first;       // first query tile that sees the block
-    int m_count;       // number of query tiles
+    // Query tiles that see the block: count0 tiles starting at first0 in the first segment
+    // (the whole document, or the front half of a zigzag shard) followed by count1 tiles
+    // starting at first1 in the second segment (the back half).
+    int first0;
+    int count0;
+    int first1;
+    int count1;
+    int seg_len;       // rows between the two segments (half length); 0 outside ring mode
+    int k_row;         // first row of the K/V block in the tensor the K/V maps cover
+    int diag_seg;      // ring mode: segment whose tile `diag_tile` is the masked diagonal (-1: none)
+    int diag_tile;
+    int owner;         // ring mode: rank that owns the K/V block
+    int owner_block;   // ring mode: 128-row block index inside the owner's slice
 };
+
+// Query tile of step t (within one head): document-local first row and whether it is the
+// masked diagonal of a ring work item.
+__device__ __forceinline__ int bwd_step_row(const BwdWork& wk, int t, bool* diag) {
+    int seg = 0, tile = wk.first0 + t;
+    if (t >= wk.count0) {
+        seg = 1;
+        tile = wk.first1 + (t - wk.count0);
+    }
+    *diag = (seg == wk.diag_seg && tile == wk.diag_tile);
+    return seg * wk.seg_len + tile * kTileM;
+}
 
 // Padded row offset of a document: every document starts on a 128-row boundary and owns
 // at least round_up(len, 128) rows.
@@ -82,6 +125,53 @@ __device__ __forceinline__ BwdWork bwd_decode_work(const BwdParams& p, int w) {
     BwdWork wk;
     int entry = w / p.heads_k;
     wk.head_k = w - entry * p.heads_k;
+    wk.first1 = 0;
+    wk.count1 = 0;
+    wk.seg_len = 0;
+    wk.diag_seg = -1;
+    wk.diag_tile = 0;
+    wk.owner = 0;
+    wk.owner_block = 0;
+    if (p.ring_docs != nullptr) {
+        const int4 e = p.ring_work[entry];
+        const RingDoc& d = p.ring_docs[e.x];
+        const int g = d.ring_size, r = d.ring_rank, s = e.y, hf = e.z, blk = e.w;
+        const int hb = d.half_len / kTileM;
+        wk.q_begin = d.q_begin;
+        wk.q_len = d.half_len;
+        wk.k_begin = 0;
+        wk.k_len = d.half_len;
+        wk.q_pad_begin = d.q_begin;
+        wk.n0 = blk * kTileN;                       // chunk-local key row
+        wk.seg_len = d.half_len;
+        wk.k_row = d.member_row[s] + hf * d.half_len + blk * kTileN;
+        wk.owner = wk.k_row / p.cap;
+        wk.owner_block = (wk.k_row - wk.owner * p.cap) / kTileN;
+        // Global chunk indices: key chunk ck, query chunks cq of the two local halves.
+        const int ck = g == 1 ? 0 : (hf == 0 ? s : 2 * g - 1 - s);
+        int first[2] = {0, 0}, count[2] = {0, 0};
+        const int halves = g == 1 ? 1 : 2;
+        for (int h = 0; h < halves; ++h) {
+            if (!p.causal) {
+                count[h] = hb;
+            } else {
+                const int cq = g == 1 ? 0 : (h == 0 ? r : 2 * g - 1 - r);
+                if (ck < cq) {
+                    count[h] = hb;
+                } else if (ck == cq) {
+                    first[h] = blk;
+                    count[h] = hb - blk;
+                    wk.diag_seg = h;
+                    wk.diag_tile = blk;
+                }
+            }
+        }
+        wk.first0 = first[0];
+        wk.count0 = count[0];
+        wk.first1 = first[1];
+        wk.count1 = count[1];
+        return wk;
+    }
     int nblk;
     if (p.cu_seqlens_q == nullptr) {
         int nnb = (p.seqlen_k + kTileN - 1) / kTileN;
@@ -111,8 +201,9 @@ __device__ __forceinline__ BwdWork bwd_decode_work(const BwdParams& p, int w) {
         int first_row = max(0, wk.n0 + wk.q_len - wk.k_len);
         first = min(m_tiles, first_row / kTileM);
     }
-    wk.m_first = first;
-    wk.m_count = m_tiles - first;
+    wk.first0 = first;
+    wk.count0 = m_tiles - first;
+    wk.k_row = wk.k_begin + wk.n0;
     return wk;
 }
 
@@ -141,10 +232,73 @@ struct __align__(1024) BwdShared {
     uint64_t dkv_empty;
     uint64_t sched_full[2];
     uint64_t sched_empty[2];
+    uint64_t comm_full[6];
+    uint64_t comm_empty[6];
     int sched_w[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
+static_assert(sizeof(BwdShared) <= 232448, "backward shared storage exceeds the 227 KiB opt-in limit");
+
+// Copy role of a ring-mode backward CTA (same protocol as the forward's): six 32 KiB slots laid
+// over the K ... dO tile buffers, one loading thread, one storing thread, per-block ready flags.
+__device__ __forceinline__ void bwd_ring_copy_role(const BwdParams& p, BwdShared& sh, const WaitCtx& wctx,
+                                                   int warp, int lane) {
+    constexpr uint32_t kSlotBytes = kTileBytes;
+    const uint32_t block_bytes = static_cast<uint32_t>(kTileN) * p.kv_row_bytes;
+    const uint32_t chunks = block_bytes / kSlotBytes;
+    const uint32_t slot_base = smem_u32(&sh.k[0]);
+    const int first = static_cast<int>(blockIdx.x) - p.num_comp;
+    const int stride = static_cast<int>(gridDim.x) - p.num_comp;
+    if (warp == 13 && lane == 0) {
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = first; t < p.comm_task_count && ok; t += stride) {
+            const int2 task = p.comm_tasks[t];
+            const size_t off = static_cast<size_t>(task.y) * block_bytes;
+            for (int kv = 0; kv < 2 && ok; ++kv) {
+                const uint8_t* src = (kv == 0 ? p.peer_k[task.x] : p.peer_v[task.x]) + off;
+                for (uint32_t c = 0; c < chunks; ++c, ++it) {
+                    const uint32_t slot = it % 6u;
+                    ok = mbar_wait(wctx, smem_u32(&sh.comm_empty[slot]), ((it / 6u) & 1u) ^ 1u, 24);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(smem_u32(&sh.comm_full[slot]), kSlotBytes);
+                    bulk_load_1d(slot_base + slot * kSlotBytes, src + static_cast<size_t>(c) * kSlotBytes,
+                                 kSlotBytes, smem_u32(&sh.comm_full[slot]));
+                }
+            }
+        }
+    } else if (warp == 14 && lane == 0) {
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = first; t < p.comm_task_count && ok; t += stride) {
+            const int2 task = p.comm_tasks[t];
+            const size_t off = static_cast<size_t>(task.y) * block_bytes;
+            for (int kv = 0; kv < 2 && ok; ++kv) {
+                uint8_t* dst = (kv == 0 ? p.arena_k : p.arena_v) + off;
+                for (uint32_t c = 0; c < chunks; ++c, ++it) {
+                    const uint32_t slot = it % 6u;
+                    ok = mbar_wait(wctx, smem_u32(&sh.comm_full[slot]), (it / 6u) & 1u, 25);
+                    if (!ok) break;
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 ::"l"(reinterpret_cast<uint64_t>(dst + static_cast<size_t>(c) * kSlotBytes)),
+                                   "r"(slot_base + slot * kSlotBytes), "r"(kSlotBytes)
+                                 : "memory");
+                    bulk_commit_group();
+                    bulk_wait_group_read<0>();
+                    mbar_arrive(smem_u32(&sh.comm_empty[slot]));
+                }
+            }
+            if (ok) {
+                bulk_wait_group<0>();
+                fence_proxy_async_all();
+                asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.kv_flags + task.y), "r"(1)
+                             : "memory");
+            }
+        }
+        bulk_wait_group<0>();
+    }
+}
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -184,6 +338,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             mbar_init(smem_u32(&sh.sched_full[i]), 1);
             mbar_init(smem_u32(&sh.sched_empty[i]), 1 + 12);   // MMA warp + 12 consumer warps
         }
+        for (int i = 0; i < 6; ++i) {
+            mbar_init(smem_u32(&sh.comm_full[i]), 1);
+            mbar_init(smem_u32(&sh.comm_empty[i]), 1);
+        }
         sh.abort_flag = 0;
         fence_mbar_init();
         fence_proxy_async_smem();
@@ -202,6 +360,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const int total_work =
         (p.cu_seqlens_q == nullptr ? p.num_entries_host : *p.num_entries_dev) * p.heads_k;
     const int group = p.heads_q / p.heads_k;
+
+    // Copy CTAs (ring mode) first pull the other ranks' K/V blocks into the local arena.
+    if (p.ring_docs != nullptr && static_cast<int>(blockIdx.x) >= p.num_comp && p.comm_task_count > 0) {
+        bwd_ring_copy_role(p, sh, wctx, warp, lane);
+        __syncthreads();
+    }
 
     if (warp >= 12) {
         reg_dealloc<88>();
@@ -230,14 +394,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 if (lane == 0) mbar_arrive(smem_u32(&sh.sched_full[slot]));
                 if (w < 0) break;
                 const BwdWork wk = bwd_decode_work(p, w);
-                const int steps = wk.m_count * group;
+                const int per_head = wk.count0 + wk.count1;
+                const int steps = per_head * group;
                 if (steps == 0) continue;
                 ok = mbar_wait(wctx, smem_u32(&sh.kv_empty), (item_cnt & 1u) ^ 1u, 2);
                 if (!ok) break;
                 ++item_cnt;
+                if (p.ring_docs != nullptr && wk.owner != p.my_rank) {
+                    ok = flag_wait(wctx, p.kv_flags + wk.k_row / kTileN, 23);
+                    if (!ok) break;
+                    fence_proxy_async_all();
+                }
                 if (lane == 0) {
                     const uint32_t bar = smem_u32(&sh.kv_full);
-                    const int row = wk.k_begin + wk.n0;
+                    const int row = wk.k_row;
                     mbar_arrive_expect_tx(bar, 2 * kTileBytes);
                     tma_load_3d(smem_u32(&sh.k[0]), &map_k, bar, 0, wk.head_k, row);
                     tma_load_3d(smem_u32(&sh.k[0]) + kHalfTileBytes, &map_k, bar, 64, wk.head_k, row);
@@ -245,8 +415,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     tma_load_3d(smem_u32(&sh.v[0]) + kHalfTileBytes, &map_v, bar, 64, wk.head_k, row);
                 }
                 for (int t = 0; t < steps && ok; ++t) {
-                    const int hq = wk.head_k * group + t / wk.m_count;
-                    const int m = wk.m_first + t % wk.m_count;
+                    const int hq = wk.head_k * group + t / per_head;
+                    bool diag;
+                    const int q_local = bwd_step_row(wk, t % per_head, &diag);
                     const uint32_t stage = step_it % kBwdStages;
                     const uint32_t par = ((step_it / kBwdStages) & 1u) ^ 1u;
                     ++step_it;
@@ -255,9 +426,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     if (lane == 0) {
                         const uint32_t bar = smem_u32(&sh.q_full[stage]);
                         const uint32_t dst = smem_u32(&sh.q[stage][0]);
-                        const int row = wk.q_begin + m * kTileM;
+                        const int row = wk.q_begin + q_local;
                         const long long vec =
-                            static_cast<long long>(hq) * p.padded_q + wk.q_pad_begin + m * kTileM;
+                            static_cast<long long>(hq) * p.padded_q + wk.q_pad_begin + q_local;
                         mbar_arrive_expect_tx(bar, kTileBytes + 2 * kRowVecBytes);
                         tma_load_3d(dst, &map_q, bar, 0, hq, row);
                         tma_load_3d(dst + kHalfTileBytes, &map_q, bar, 64, hq, row);
@@ -269,7 +440,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     if (lane == 0) {
                         const uint32_t bar = smem_u32(&sh.do_full[stage]);
                         const uint32_t dst = smem_u32(&sh.dout[stage][0]);
-                        const int row = wk.q_begin + m * kTileM;
+                        const int row = wk.q_begin + q_local;
                         mbar_arrive_expect_tx(bar, kTileBytes);
                         tma_load_3d(dst, &map_do, bar, 0, hq, row);
                         tma_load_3d(dst + kHalfTileBytes, &map_do, bar, 64, hq, row);
@@ -309,7 +480,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 if (lane == 0) mbar_arrive(smem_u32(&sh.sched_empty[slot]));
                 if (w < 0) break;
                 const BwdWork wk = bwd_decode_work(p, w);
-                const int steps = wk.m_count * group;
+                const int steps = (wk.count0 + wk.count1) * group;
                 if (steps == 0) continue;
                 ok = mbar_wait(wctx, smem_u32(&sh.kv_full), item_cnt & 1u, 6);
                 if (!ok) break;
@@ -443,13 +614,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             if (lane == 0) mbar_arrive(smem_u32(&sh.sched_empty[slot]));
             if (w < 0) break;
             const BwdWork wk = bwd_decode_work(p, w);
-            const int steps = wk.m_count * group;
+            const int per_head = wk.count0 + wk.count1;
+            const int steps = per_head * group;
             const int pad_tiles = p.padded_q / kTileM;
             for (int t = 0; t < steps && ok; ++t) {
-                const int hq = wk.head_k * group + t / wk.m_count;
-                const int m = wk.m_first + t % wk.m_count;
+                const int hq = wk.head_k * group + t / per_head;
+                bool diag;
+                const int q_local = bwd_step_row(wk, t % per_head, &diag);
                 float* tile = p.dq_accum +
-                              (static_cast<long long>(hq) * pad_tiles + wk.q_pad_begin / kTileM + m) *
+                              (static_cast<long long>(hq) * pad_tiles + (wk.q_pad_begin + q_local) / kTileM) *
                                   kDqTileFloats;
                 ok = mbar_wait(wctx, smem_u32(&sh.dq_full), dq_cnt & 1u, 16);
                 if (!ok) break;
@@ -502,19 +675,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             if (lane == 0) mbar_arrive(smem_u32(&sh.sched_empty[slot]));
             if (w < 0) break;
             const BwdWork wk = bwd_decode_work(p, w);
-            const int steps = wk.m_count * group;
+            const int per_head = wk.count0 + wk.count1;
+            const int steps = per_head * group;
+            const bool ring = p.ring_docs != nullptr;
             const int kv_row = wk.n0 + i_row;
             const bool kv_valid = kv_row < wk.k_len;
             const int shift = wk.k_len - wk.q_len;     // key c visible to query r iff c <= r + shift
 
             for (int t = 0; t < steps && ok; ++t) {
-                const int m = wk.m_first + t % wk.m_count;
+                bool diag;
+                const int q_local = bwd_step_row(wk, t % per_head, &diag);
                 const uint32_t stage = step_it % kBwdStages;
                 const uint32_t par = (step_it / kBwdStages) & 1u;
                 ++step_it;
-                const int q0 = m * kTileM + wg * 64;   // document-local query row of column 0
+                // Query row of column 0, in the coordinates of the key rows (document-local, or
+                // chunk-local for the diagonal tile of a ring work item).
+                const int q0 = (ring ? q_local - (q_local >= wk.seg_len ? wk.seg_len : 0) : q_local) + wg * 64;
                 // Columns c < c_min are hidden from this key row by the causal rule.
-                const int c_min = p.causal ? (kv_row - shift - q0) : 0;
+                const int c_min = (ring ? diag : p.causal != 0) ? (kv_row - shift - q0) : 0;
                 const bool need_mask = !kv_valid || c_min > 0;
 
                 // LSE2 / D of this tile arrive with Q.
@@ -638,7 +816,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0u;
                 }
-                if (kv_valid) {
+                if (ring) {
+                    // Owner-directed accumulation: add this rank's partial dK / dV tile into the
+                    // fp32 accumulator of the rank that owns the key block (possibly over NVLink).
+                    float* acc = (wg == 0 ? p.dv_accum_peer[wk.owner] : p.dk_accum_peer[wk.owner]) +
+                                 (static_cast<long long>(wk.owner_block) * p.heads_k + wk.head_k) * kDqTileFloats;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float* dst = acc + ((c * 8 + i) * kTileM + i_row) * 4;
+                        asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                     ::"l"(dst), "f"(__uint_as_float(v[4 * i]) * mul),
+                                       "f"(__uint_as_float(v[4 * i + 1]) * mul),
+                                       "f"(__uint_as_float(v[4 * i + 2]) * mul),
+                                       "f"(__uint_as_float(v[4 * i + 3]) * mul)
+                                     : "memory");
+                    }
+                } else if (kv_valid) {
                     uint4* dst = reinterpret_cast<uint4*>(dst_base + c * 32);
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
@@ -659,11 +852,26 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
     }
 
+    if (p.ring_docs != nullptr) {
+        __threadfence_system();   // this thread's peer adds are performed before the CTA reports
+    }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 12) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
+    }
+    if (p.ring_docs != nullptr && threadIdx.x == 0) {
+        // The last CTA of this rank tells every rank (itself included) that all of this rank's
+        // dK / dV contributions have been added.
+        const int done = atomicAdd(p.done_ctas, 1);
+        if (done == static_cast<int>(gridDim.x) - 1) {
+            __threadfence_system();
+            for (int r = 0; r < p.world; ++r) {
+                asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p.completion_peer[r]), "r"(1)
+                             : "memory");
+            }
+        }
     }
 }
 
@@ -762,6 +970,10 @@ struct BwdPostParams {
     int heads_q;
     int padded_q;
     float scale;
+    // Accumulator tile of (head h, padded 128-row tile t) = h * tile_head_stride + t * tile_row_stride
+    // (0, 0 selects the dq_accum layout: h * padded_q / 128 + t).
+    int tile_head_stride;
+    int tile_row_stride;
 };
 
 __global__ void __launch_bounds__(128)
@@ -795,8 +1007,10 @@ bwd_postprocess_kernel(const BwdPostParams p) {
     const int r0 = prow0 - pad_begin;
     if (r0 >= q_len) return;
 
-    const float4* src = reinterpret_cast<const float4*>(
-        p.dq_accum + (static_cast<long long>(h) * pad_tiles + pad_tile) * kDqTileFloats);
+    const long long tile_index = p.tile_row_stride == 0
+        ? static_cast<long long>(h) * pad_tiles + pad_tile
+        : static_cast<long long>(h) * p.tile_head_stride + static_cast<long long>(pad_tile) * p.tile_row_stride;
+    const float4* src = reinterpret_cast<const float4*>(p.dq_accum + tile_index * kDqTileFloats);
     // src[chunk * 128 + row] holds columns 4*chunk .. 4*chunk+3 of `row`.  Two passes of 64
     // columns each keep the transposition buffer inside static shared memory.
     const int sub = threadIdx.x & 7;
@@ -822,6 +1036,32 @@ bwd_postprocess_kernel(const BwdPostParams p) {
             }
         }
         __syncthreads();
+    }
+}
+
+// Waits (bounded) until a system-scope counter reaches `expected`: every rank adds one to every
+// rank's counter when all of its dK / dV contributions have been added.
+__global__ void ring_wait_kernel(const int* counter, int expected, unsigned int* status,
+                                 unsigned long long timeout_ns) {
+    const uint64_t start = global_timer_ns();
+    while (true) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= expected) return;
+        if (global_timer_ns() - start > timeout_ns) {
+            set_status(status, kStatusTimeout, (26u << 12));
+            return;
+        }
+        __nanosleep(500);
+    }
+}
+
+// Completion report of a rank that launched no attention work.
+__global__ void ring_signal_kernel(int* c0, int* c1, int* c2, int* c3, int* c4, int* c5, int* c6, int* c7,
+                                   int world) {
+    int* c[8] = {c0, c1, c2, c3, c4, c5, c6, c7};
+    for (int r = 0; r < world; ++r) {
+        asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(c[r]), "r"(1) : "memory");
     }
 }
 

@@ -25,6 +25,7 @@ __all__ = [
     "forward_varlen_mega_ring",
     "backward",
     "backward_varlen",
+    "backward_varlen_mega_ring",
     "create_parallel_tensor",
     "parallel_remote_load",
     "parallel_remote_load_vec",
@@ -409,4 +410,5 @@ def backward_varlen(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: tor
 # re-exported here so that this module carries the whole reference API surface.
 from .parallel import (TKParallelTensor, _resolve_parallel_context, create_parallel_tensor,  # noqa: E402,F401
                        parallel_remote_load, parallel_remote_load_vec)
-from .ring import forward_varlen_mega_ring, forward_varlen_ring  # noqa: E402,F401
+from .ring import (backward_varlen_mega_ring, forward_varlen_mega_ring,  # noqa: E402,F401
+                   forward_varlen_ring)

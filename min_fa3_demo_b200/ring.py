@@ -21,7 +21,7 @@ from .min_fa3_op import (_INT32_MAX, _call_fwd, _check, _check_cu_seqlens, _chec
                          _check_device_capability, _check_varlen_qkv, _stream_ptr, _workspace)
 from .parallel import TKParallelTensor
 
-__all__ = ["forward_varlen_ring", "forward_varlen_mega_ring"]
+__all__ = ["forward_varlen_ring", "forward_varlen_mega_ring", "backward_varlen_mega_ring"]
 
 
 def _check_parallel_base(t: TKParallelTensor, name: str) -> None:
@@ -316,3 +316,108 @@ def forward_varlen_mega_ring(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, 
     if return_lse:
         return out, lse
     return out
+
+
+# --------------------------------------------------------------------------------------
+# context-parallel backward
+# --------------------------------------------------------------------------------------
+def _check_parallel_identity(t: TKParallelTensor, q: torch.Tensor, world: int, rank: int, name: str) -> None:
+    # reference: csrc/backward/min_fa3_bwd_bindings.cu:359-373
+    _check(isinstance(t, TKParallelTensor), f"{name} must be a TKParallelTensor")
+    _check(t.data_.is_cuda, f"{name} must be CUDA-backed")
+    _check(t.data_.device == q.device, f"{name} local view must be on q.device")
+    _check(t.local_world_size_ == world, f"{name} world size mismatch")
+    _check(t.local_rank_ == rank, f"{name} local rank mismatch")
+    _check(len(t.raw_ptrs_) == world, f"{name} must expose one pointer per rank")
+
+
+def backward_varlen_mega_ring(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
+                              max_seqlen_k, *, cu_seqlens_q_host, cu_seqlens_k_host,
+                              remote_k: TKParallelTensor, remote_v: TKParallelTensor,
+                              remote_dk_accum: TKParallelTensor, remote_dv_accum: TKParallelTensor,
+                              remote_dkv_completion: TKParallelTensor, num_comp_sm: int, num_comm_sm: int,
+                              global_seqlens_host, ring_sizes_host, ring_starts_host, is_causal: bool = True
+                              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Context-parallel backward of ``forward_varlen_mega_ring`` (reference:
+    ``backward_varlen_mega_ring``, csrc/backward/min_fa3_bwd_bindings.cu:375-722; causal like the
+    reference by default, the non-causal ring is accepted too).
+
+    ``k`` / ``v`` are the K/V arenas (``remote_k.data_`` / ``remote_v.data_``).  The fp32
+    accumulators ``remote_dk_accum`` / ``remote_dv_accum`` (>= ``KVH * rank_kv_capacity * 128``
+    floats) and the int32 ``remote_dkv_completion`` counter must be zeroed, and all ranks
+    synchronised, before every call.  Returns ``dq [total_q, QH, 128]`` and compact
+    ``dk, dv [local_total_k, KVH, 128]``."""
+    from .min_fa3_op import _check_bf16_cuda, _check_same_device
+    max_seqlen_q, max_seqlen_k = int(max_seqlen_q), int(max_seqlen_k)
+    num_comp_sm, num_comm_sm = int(num_comp_sm), int(num_comm_sm)
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (out, "out"), (dout, "dout")):
+        _check_bf16_cuda(t, name, 3)
+    _check(softmax_lse.is_cuda and softmax_lse.dtype == torch.float32 and softmax_lse.is_contiguous(),
+           "softmax_lse must be a contiguous CUDA float32 tensor")
+    _check(tuple(softmax_lse.shape) == (q.size(1), q.size(0)), "softmax_lse must have shape [QH, total_q]")
+    for t, name in ((k, "k"), (v, "v"), (out, "out"), (dout, "dout"), (softmax_lse, "softmax_lse")):
+        _check_same_device(q, t, name)
+    _check(out.shape == q.shape, "out must have the same shape as q")
+    _check(dout.shape == q.shape, "dout must have the same shape as q")
+    _check(k.size(1) == v.size(1), "k and v must have the same KV head count")
+    _check(q.size(1) % k.size(1) == 0, "qhead must be divisible by kvhead")
+    _check_cu_seqlens(cu_seqlens_q, "cu_seqlens_q")
+    _check_cu_seqlens(cu_seqlens_k, "cu_seqlens_k")
+    _check_cu_seqlens_host(cu_seqlens_q_host, cu_seqlens_q, "cu_seqlens_q_host")
+    _check_cu_seqlens_host(cu_seqlens_k_host, cu_seqlens_k, "cu_seqlens_k_host")
+    _check(num_comp_sm > 0, f"num_comp_sm must be positive. Got {num_comp_sm}")
+    _check(num_comm_sm >= 0, f"num_comm_sm must be non-negative. Got {num_comm_sm}")
+    _check_parallel_base(remote_k, "remote_k")
+    _check_parallel_base(remote_v, "remote_v")
+    world, rank = _ring_arena_checks(q, k, v, remote_k, remote_v, "mega ring backward", (1, 2, 4, 8))
+    for t, name in ((remote_dk_accum, "remote_dk_accum"), (remote_dv_accum, "remote_dv_accum"),
+                    (remote_dkv_completion, "remote_dkv_completion")):
+        _check_parallel_identity(t, q, world, rank, name)
+    _check(remote_dk_accum.data_.dtype == torch.float32 and remote_dv_accum.data_.dtype == torch.float32,
+           "remote_dk_accum and remote_dv_accum must have dtype torch.float32")
+    _check(remote_dkv_completion.data_.dtype == torch.int32 and remote_dkv_completion.data_.numel() >= 1,
+           "remote_dkv_completion must be an int32 tensor with at least one element")
+    _check_device_capability(q.device, "min_fa3_demo_b200 backward")
+    sm_count = torch.cuda.get_device_properties(q.device).multi_processor_count
+    _check(num_comp_sm + num_comm_sm <= sm_count,
+           f"num_comp_sm + num_comm_sm must not exceed the device SM count ({sm_count}). "
+           f"Got {num_comp_sm + num_comm_sm}")
+    cap = _validate_ring_metadata(q, k, cu_seqlens_q_host, cu_seqlens_k_host, global_seqlens_host,
+                                  ring_sizes_host, ring_starts_host, world, rank, bool(is_causal),
+                                  max_seqlen_q, max_seqlen_k)
+    need = k.size(1) * cap * 128
+    _check(remote_dk_accum.data_.numel() >= need and remote_dv_accum.data_.numel() >= need,
+           f"remote_dk_accum / remote_dv_accum need at least KVH * rank_kv_capacity * 128 = {need} floats")
+    batch = cu_seqlens_q_host.size(0) - 1
+    local_total_k = int(cu_seqlens_k_host[batch])
+
+    dq = torch.empty_like(q)
+    dk = torch.empty((local_total_k, k.size(1), 128), dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty_like(dk)
+    lib = _cabi.load()
+    nbytes = lib.b2a_ring_bwd_workspace_bytes(batch, world, cap, q.size(0), q.size(1))
+    ws = _workspace(nbytes, q.device)
+    a = _cabi.RingBwdArgs()
+    a.dout, a.q, a.out, a.lse = dout.data_ptr(), q.data_ptr(), out.data_ptr(), softmax_lse.data_ptr()
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.arena_k, a.arena_v = k.data_ptr(), v.data_ptr()
+    for r in range(world):
+        a.peer_k[r] = remote_k.raw_ptrs_[r]
+        a.peer_v[r] = remote_v.raw_ptrs_[r]
+        a.dk_accum_peer[r] = remote_dk_accum.raw_ptrs_[r]
+        a.dv_accum_peer[r] = remote_dv_accum.raw_ptrs_[r]
+        a.completion_peer[r] = remote_dkv_completion.raw_ptrs_[r]
+    a.cu_seqlens_q_host = cu_seqlens_q_host.data_ptr()
+    a.global_seqlens_host = global_seqlens_host.data_ptr()
+    a.ring_sizes_host = ring_sizes_host.data_ptr()
+    a.ring_starts_host = ring_starts_host.data_ptr()
+    a.batch, a.world_size, a.rank, a.rank_kv_capacity = batch, world, rank, cap
+    a.total_q, a.local_total_k = q.size(0), local_total_k
+    a.heads_q, a.heads_k, a.head_dim = q.size(1), k.size(1), 128
+    a.is_causal = int(bool(is_causal))
+    a.num_comp_sm, a.num_comm_sm = num_comp_sm, num_comm_sm
+    a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+    with torch.cuda.device(q.device):
+        _cabi.check(lib.b2a_ring_bwd(ctypes.byref(a), _stream_ptr(q.device)))
+    backward_varlen_mega_ring.last_workspace = ws
+    return dq, dk, dv

@@ -250,7 +250,67 @@ def case_ring_steps(rank, world, dev):
         barrier(world)
 
 
-CASES = {"mega_ring_fwd": case_mega_ring_fwd, "remote_load": case_remote_load, "ring_steps": case_ring_steps}
+def case_mega_ring_bwd(rank, world, dev):
+    """dQ / dK / dV of the context-parallel backward against fp32 autograd over the global
+    documents (dense reference as in ...backward_multi_rank.py:95-122, oracle-side)."""
+    from min_fa3_demo_b200.min_fa3_op import check_device_status
+    qh, kvh = 8, 2
+    sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    for causal in (True, False):
+        docs = ring_docs_for(world)
+        q, k, v, dout, cu, odocs = build_problem(world, rank, docs, qh, kvh, causal, BASE_SEED + 11 + causal)
+        cap = 2048
+        rk, rv = make_arena(world, rank, cap, k, v, dev)
+        acc_k = min_fa3_op.TKParallelTensor([kvh * cap * 128], torch.float32, dev.index, world, False)
+        acc_v = min_fa3_op.TKParallelTensor([kvh * cap * 128], torch.float32, dev.index, world, False)
+        done = min_fa3_op.TKParallelTensor([1], torch.int32, dev.index, world, False)
+        g, s, st = meta(docs)
+        lens = (cu[1:] - cu[:-1]).tolist()
+        mx = max(max(lens), 1)
+        qd, dd, cud = q.to(dev), dout.to(dev), cu.to(dev)
+        barrier(world)
+        ok = True
+        for rep in range(2):
+            out, lse = min_fa3_op.forward_varlen_mega_ring(
+                qd, rk.data_, rv.data_, cud, cud, mx, mx, causal, cu_seqlens_q_host=cu, cu_seqlens_k_host=cu,
+                remote_k=rk, remote_v=rv, num_comp_sm=sm - 8, num_comm_sm=8, global_seqlens_host=g,
+                ring_sizes_host=s, ring_starts_host=st, return_lse=True)
+            acc_k.data_.zero_(); acc_v.data_.zero_(); done.data_.zero_()
+            barrier(world)
+            dq, dk, dv = min_fa3_op.backward_varlen_mega_ring(
+                dd, qd, rk.data_, rv.data_, out, lse, cud, cud, mx, mx, cu_seqlens_q_host=cu,
+                cu_seqlens_k_host=cu, remote_k=rk, remote_v=rv, remote_dk_accum=acc_k, remote_dv_accum=acc_v,
+                remote_dkv_completion=done, num_comp_sm=sm - 8, num_comm_sm=8, global_seqlens_host=g,
+                ring_sizes_host=s, ring_starts_host=st, is_causal=causal)
+            torch.cuda.synchronize()
+            try:
+                check_device_status(min_fa3_op.backward_varlen_mega_ring.last_workspace)
+            except RuntimeError as exc:
+                print(f"[rank {rank}] device status: {exc}", flush=True)
+                ok = False
+            ok = ok and done.data_.item() == world
+            # reference gradients: autograd over each global document, then this rank's rows
+            rq, rkk, rvv = [], [], []
+            for (qg, kg, vg, dg, pos) in odocs:
+                qf, kf, vf = (t.float().requires_grad_() for t in (qg, kg, vg))
+                n = qg.size(0)
+                p_all = torch.arange(n)
+                o, _ = orc.attention_positions(qf, kf, vf, p_all if causal else None, p_all if causal else None)
+                gq, gk, gv = torch.autograd.grad(o, (qf, kf, vf), dg.float())
+                rq.append(gq[pos]); rkk.append(gk[pos]); rvv.append(gv[pos])
+            if rq:
+                for name, got, ref in (("dq", dq, torch.cat(rq)), ("dk", dk, torch.cat(rkk)), ("dv", dv, torch.cat(rvv))):
+                    err = (got.float().cpu() - ref).abs().max().item()
+                    tol = 4e-2 * max(1.0, ref.abs().max().item())
+                    if not err <= tol:
+                        print(f"[rank {rank}] causal={causal} rep={rep} {name}: err {err:.3e} tol {tol:.3e}", flush=True)
+                        ok = False
+            barrier(world)
+        vote(ok, world, f"mega_ring_bwd causal={causal} world={world}", rank)
+        barrier(world)
+
+
+CASES = {"mega_ring_bwd": case_mega_ring_bwd, "mega_ring_fwd": case_mega_ring_fwd, "remote_load": case_remote_load, "ring_steps": case_ring_steps}
 
 
 def main(argv):
