@@ -1,0 +1,83 @@
+"""Placement planner: legality, ordering, determinism and balance quality against recorded
+results of the reference planner (tests/golden/balancer_reference.json, written by
+tests/golden/make_balancer_golden.py)."""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import pytest
+
+from min_fa3_demo_b200 import balancer as bal
+
+CASES = json.loads((Path(__file__).resolve().parent / "golden" / "balancer_reference.json").read_text())
+
+
+def test_eligible_ring_sizes_follow_the_reference_rule():
+    # causal: G > 1 needs length % (256 * G) == 0 (balancer/load_balancer.py:121-131)
+    assert bal.eligible_ring_sizes(2048, 8, True) == [1, 2, 4, 8]
+    assert bal.eligible_ring_sizes(1024, 8, True) == [1, 2, 4]
+    assert bal.eligible_ring_sizes(768, 8, True) == [1]
+    assert bal.eligible_ring_sizes(768, 4, False) == [1, 2, 4]
+    assert bal.eligible_ring_sizes(4096, 2, True) == [1, 2]
+
+
+def test_alignment_tiers():
+    assert bal.align_sequence_length(1) == 256
+    assert bal.align_sequence_length(2047) == 2048
+    assert bal.align_sequence_length(2049) == 2560
+    assert bal.align_sequence_length(5000) == 5120
+    assert bal.align_sequence_length(9000) == 10240
+    assert bal.align_sequence_length(20000) == 20480
+    assert bal.align_sequence_length(10**7) == bal.MAX_SEQUENCE_TOKENS
+
+
+def test_argument_validation():
+    with pytest.raises(ValueError, match="world_size must be 2, 4, or 8"):
+        bal.assign_hierarchical_rings([1024], 3, True)
+    with pytest.raises(ValueError, match="positive integers"):
+        bal.assign_hierarchical_rings([1024, 0], 4, True)
+    with pytest.raises(ValueError, match="compute_balance_tolerance"):
+        bal.assign_hierarchical_rings([1024], 4, True, compute_balance_tolerance=-1.0)
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"w{c['world_size']}-s{c['seed']}-{'c' if c['is_causal'] else 'n'}")
+def test_placement_is_legal_ordered_deterministic_and_balanced(case):
+    lengths, world, causal = case["lengths"], case["world_size"], case["is_causal"]
+    plan = bal.assign_hierarchical_rings(lengths, world, causal)
+    again = bal.assign_hierarchical_rings(lengths, world, causal)
+    assert (plan.global_lengths, plan.ring_sizes, plan.ring_starts) == \
+        (again.global_lengths, again.ring_sizes, again.ring_starts)
+    # every document placed exactly once
+    assert sorted(plan.original_indices) == list(range(len(lengths)))
+    assert [lengths[i] for i in plan.original_indices] == plan.global_lengths
+    # legal buddy rings, sorted by (-ring size, ring start, original index)
+    keys = []
+    for length, g, s, idx in zip(plan.global_lengths, plan.ring_sizes, plan.ring_starts, plan.original_indices):
+        assert g in bal.eligible_ring_sizes(length, world, causal)
+        assert s % g == 0 and 0 <= s and s + g <= world
+        keys.append((-g, s, idx))
+    assert keys == sorted(keys)
+    # per-rank accounting is consistent
+    assert sum(plan.rank_tokens) == sum(lengths)
+    assert sum(plan.rank_compute) == pytest.approx(sum(bal.attention_compute(l, causal) for l in lengths))
+    # quality: feasible whenever the reference planner is, without excessive extra communication
+    if case["ref_feasible"]:
+        assert plan.feasible
+        assert plan.compute_deviation <= plan.compute_balance_tolerance + 1e-9
+        assert plan.token_deviation <= plan.token_balance_tolerance + 1e-9
+    assert sum(plan.rank_communication) <= 2.2 * case["ref_communication"] + 1.0
+
+
+def test_mixture_sampler_and_local_layout():
+    lengths = bal.sample_mixture_lengths(0)
+    assert lengths == bal.sample_mixture_lengths(0)
+    assert sum(lengths) >= 131072 and all(l % 256 == 0 and l <= bal.MAX_SEQUENCE_TOKENS for l in lengths)
+    plan = bal.assign_hierarchical_rings(lengths, 8, True)
+    total = 0
+    for rank in range(8):
+        lens, cu = bal.local_layout(plan, rank)
+        assert cu[-1] == sum(lens) == plan.rank_tokens[rank]
+        assert all(l % 128 == 0 for l in lens)
+        total += cu[-1]
+    assert total == sum(lengths)
