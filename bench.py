@@ -354,6 +354,144 @@ def run_cuda_arm(args) -> None:
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------
+# Ring context-parallel workload (BASELINE config 4)
+# --------------------------------------------------------------------------------------
+def run_ring_workload(args) -> None:
+    """One 131,072-token causal sequence (QH=32, KVH=8, d=128), zigzag-sharded over the N ranks;
+    K/V of the other ranks is pulled over NVLink inside the attention launch.  Strong scaling:
+    the problem is fixed, so whole-job TFLOPS = total FLOPs / max-over-ranks time.  Forward and
+    backward are timed separately and summed; the backward time excludes the forward and the
+    accumulator zeroing + barrier that must precede every backward call (the reference's protocol,
+    ring_test/homogeneous_all_cp_microbench/benchmark_ring_backward.py:413-446)."""
+    import torch.distributed as dist
+
+    import min_fa3_op
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    total, qh, kvh = args.ring_tokens, 32, 8
+    local = total // world
+    sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    q = torch.randn(local, qh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    k = torch.randn(local, kvh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn(local, kvh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    dout = torch.randn(local, qh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    cu = torch.tensor([0, local], dtype=torch.int32)
+    cud = cu.to(dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    if world == 1:
+        def fwd():
+            return min_fa3_op.forward_varlen(q, k, v, cud, cud, local, local, True, cu_seqlens_q_host=cu,
+                                             cu_seqlens_k_host=cu, return_lse=True)
+
+        def bwd(out, lse):
+            return min_fa3_op.backward_varlen(dout, q, k, v, out, lse, cud, cud, local, local, True)
+
+        def reset():
+            pass
+    else:
+        arena_k = torch.zeros(world * local, kvh, 128, dtype=torch.bfloat16, device=dev)
+        arena_v = torch.zeros_like(arena_k)
+        arena_k[rank * local:(rank + 1) * local] = k
+        arena_v[rank * local:(rank + 1) * local] = v
+        rk = min_fa3_op.TKParallelTensor(arena_k, local_rank=local_rank, local_world_size=world, multicast=False)
+        rv = min_fa3_op.TKParallelTensor(arena_v, local_rank=local_rank, local_world_size=world, multicast=False)
+        acc_k = min_fa3_op.TKParallelTensor([kvh * local * 128], torch.float32, local_rank, world, False)
+        acc_v = min_fa3_op.TKParallelTensor([kvh * local * 128], torch.float32, local_rank, world, False)
+        done = min_fa3_op.TKParallelTensor([1], torch.int32, local_rank, world, False)
+        meta = dict(global_seqlens_host=torch.tensor([total], dtype=torch.int32),
+                    ring_sizes_host=torch.tensor([world], dtype=torch.int32),
+                    ring_starts_host=torch.tensor([0], dtype=torch.int32))
+        comm = args.ring_comm_sm
+
+        def fwd():
+            return min_fa3_op.forward_varlen_mega_ring(
+                q, rk.data_, rv.data_, cud, cud, local, local, True, cu_seqlens_q_host=cu, cu_seqlens_k_host=cu,
+                remote_k=rk, remote_v=rv, num_comp_sm=sm - comm, num_comm_sm=comm, return_lse=True, **meta)
+
+        def bwd(out, lse):
+            return min_fa3_op.backward_varlen_mega_ring(
+                dout, q, rk.data_, rv.data_, out, lse, cud, cud, local, local, cu_seqlens_q_host=cu,
+                cu_seqlens_k_host=cu, remote_k=rk, remote_v=rv, remote_dk_accum=acc_k, remote_dv_accum=acc_v,
+                remote_dkv_completion=done, num_comp_sm=sm - comm, num_comm_sm=comm, **meta)
+
+        def reset():
+            acc_k.data_.zero_()
+            acc_v.data_.zero_()
+            done.data_.zero_()
+            barrier()
+
+    barrier()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    fwd_ms, bwd_ms = [], []
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for it in range(max(args.warmup, 3) + args.steps):
+        if it == max(args.warmup, 3):
+            sampler.mark_begin()
+        barrier()
+        e[0].record()
+        out, lse = fwd()
+        e[1].record()
+        reset()
+        e[2].record()
+        bwd(out, lse)
+        e[3].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)   # per-iteration max over ranks
+        if it >= max(args.warmup, 3):
+            fwd_ms.append(t[0].item())
+            bwd_ms.append(t[1].item())
+    sampler.mark_end()
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        vis = total * (total + 1) / 2
+        f_flops, b_flops = 4.0 * qh * 128 * vis, 10.0 * qh * 128 * vis
+        fm, bm = statistics.mean(fwd_ms), statistics.mean(bwd_ms)
+        burst, sustained, peak_kind = measured_peaks()
+        value = (f_flops + b_flops) / ((fm + bm) * 1e-3) / 1e12
+        # K/V bytes rank 0 pulls per forward: front halves of all other ranks (+ back halves of
+        # ranks after it): rank 0 pulls everything = (N-1) * local rows of K and V.
+        ingress = (world - 1) * local * kvh * 128 * 2 * 2
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": fm + bm, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"ring_cp_causal_S{total}_QH32_KVH8_D128", "tokens_per_gpu": local,
+                       "parallelism": f"cp{world} zigzag ring, K/V pulled over NVLink in-kernel"
+                       if world > 1 else "single GPU (efficiency baseline)",
+                       "copy_ctas": args.ring_comm_sm if world > 1 else 0,
+                       "l2": "inputs larger than L2"},
+            "tflops_per_gpu": value / world, "fwd_ms": fm, "bwd_ms": bm,
+            "fwd_tflops_per_gpu": f_flops / (fm * 1e-3) / 1e12 / world,
+            "bwd_tflops_per_gpu": b_flops / (bm * 1e-3) / 1e12 / world,
+            "pct_of_bf16_peak": {f"{peak_kind}_burst": 100.0 * value / world / burst,
+                                 f"{peak_kind}_sustained": 100.0 * value / world / sustained if sustained else None,
+                                 "nominal_dense_2250": 100.0 * value / world / NOMINAL_BF16_TFLOPS},
+            "nvlink": {"kv_ingress_bytes_rank0_fwd": ingress,
+                       "achieved_gbs_over_fwd_kernel": ingress / (fm * 1e-3) / 1e9 if world > 1 else 0.0},
+            "gpu_launches": 4 * args.steps, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -364,6 +502,10 @@ def main() -> None:
                         help="time budget of the CPU baseline sample (N=1 only)")
     parser.add_argument("--batch", type=int, default=None,
                         help="override the per-GPU batch (smaller cases for profiler captures)")
+    parser.add_argument("--workload", choices=("bshd", "ring"), default="bshd",
+                        help="bshd: config 2 replicas (default); ring: one long causal sequence over N ranks")
+    parser.add_argument("--ring-tokens", type=int, default=131072)
+    parser.add_argument("--ring-comm-sm", type=int, default=8)
     parser.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
     parser.add_argument("--skip-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
     args = parser.parse_args()
@@ -372,6 +514,8 @@ def main() -> None:
         WORKLOAD["name"] = WORKLOAD["name"].replace("_B4_", f"_B{args.batch}_")
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "ring":
+        run_ring_workload(args)
     else:
         run_cuda_arm(args)
 
