@@ -119,7 +119,8 @@ def ring_docs_for(world: int):
     """A hierarchical mix: all-rank documents, sub-rings, single-rank documents."""
     docs = [(world * 512, world, 0), (world * 256, world, 0)]
     if world >= 4:
-        docs += [(1024, world // 2, 0), (512, world // 2, world // 2)]
+        half = world // 2
+        docs += [(half * 512, half, 0), (half * 256, half, half)]
     if world >= 2:
         docs += [(512, 1, 0), (256, 1, world - 1), (128, 1, 1 % world)]
     else:
