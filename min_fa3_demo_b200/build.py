@@ -35,6 +35,11 @@ NVCC_FLAGS = [
 ]
 
 
+def extra_flags() -> list[str]:
+    """Additional nvcc flags from the environment (e.g. -DB2A_PHASES for phase timing probes)."""
+    return os.environ.get("B2A_EXTRA_NVCC_FLAGS", "").split()
+
+
 def find_nvcc() -> str:
     cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     candidate = Path(cuda_home) / "bin" / "nvcc"
@@ -56,7 +61,7 @@ def _digest() -> str:
                        + [PKG_DIR.parent / "include" / "b200attn.h"]):
         h.update(path.name.encode())
         h.update(path.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + extra_flags()).encode())
     return h.hexdigest()
 
 
@@ -75,7 +80,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(src: Path) -> Path:
         obj = BUILD_DIR / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *extra_flags(), *extra, "-c", str(src), "-o", str(obj)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or res.returncode != 0:
             sys.stderr.write(f"$ {' '.join(cmd)}\n{res.stdout}{res.stderr}")

@@ -4,6 +4,7 @@
 #include "b2a_ring_host.cuh"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace b2a {
@@ -11,6 +12,20 @@ namespace b2a {
 namespace {
 
 constexpr size_t kBwdSmemBytes = sizeof(BwdShared);
+
+// Key/value heads scheduled together: as many as keep the fp32 dQ accumulator tiles that the
+// concurrently running CTAs add into (heads x query rows x 512 bytes) within a share of L2.
+int pick_sg_heads(int heads_q, int heads_k, long long q_rows) {
+    if (const char* env = getenv("B2A_BWD_SG_HEADS")) {
+        const int v = atoi(env);
+        if (v >= 1) return v < heads_k ? v : heads_k;
+    }
+    const long long per_head = static_cast<long long>(heads_q / heads_k) * (q_rows > 0 ? q_rows : 1) * 512;
+    const long long budget = 48ll << 20;
+    long long n = budget / per_head;
+    if (n < 1) n = 1;
+    return n < heads_k ? static_cast<int>(n) : heads_k;
+}
 
 struct BwdLayout {
     size_t work_list_off;
@@ -185,6 +200,7 @@ int b2a_bwd(const b2a_bwd_args* a, void* cuda_stream) {
     p.scale_log2 = scale * kLog2e;
     p.timeout_ns = kDefaultTimeoutNs;
 
+    p.sg_heads = pick_sg_heads(a->heads_q, a->heads_k, varlen ? a->total_q : a->seqlen_q);
     long long work_items;
     if (varlen) {
         rc = launch_varlen_plan(1, a->cu_seqlens_q, a->cu_seqlens_k, a->batch, causal, work_list,
@@ -404,6 +420,7 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
         p.heads_k = a->heads_k;
         p.causal = causal;
         p.num_entries_host = static_cast<int>(entries.size());
+        p.sg_heads = pick_sg_heads(a->heads_q, a->heads_k, a->total_q);
         p.padded_q = a->total_q;
         p.scale = scale;
         p.scale_log2 = scale * kLog2e;

@@ -28,7 +28,10 @@
 namespace b2a {
 
 constexpr int kBwdThreads = 512;
-constexpr int kBwdStages = 2;          // Q / dO ring stages
+constexpr int kBwdStages = 2;          // Q ring stages (with their LSE2 / D vectors)
+constexpr int kDoStages = 1;           // dO is single-buffered: it lives only from dP(t) to dV(t)
+constexpr uint32_t kDqBarrier = 1;          // named barrier of the dQ warpgroup
+constexpr uint32_t kDqChunkBytes = 16384;   // 32 dQ columns x 128 rows fp32: one bulk reduction
 constexpr uint32_t kRowVecBytes = kTileM * 4;   // 128 fp32 (LSE2 or D of one query tile)
 
 // dq_accum layout: [head][padded 128-row tile][32 column chunks][128 rows][4 floats], so a
@@ -54,6 +57,7 @@ struct BwdParams {
     int heads_k;
     int causal;
     int num_entries_host;
+    int sg_heads;      // key/value heads per scheduling supergroup (1..heads_k)
     int padded_q;                  // padded query rows per head (multiple of 128)
     float scale;
     float scale_log2;
@@ -123,8 +127,25 @@ __host__ __device__ __forceinline__ int bwd_padded_begin(int cu_begin, int doc) 
 
 __device__ __forceinline__ BwdWork bwd_decode_work(const BwdParams& p, int w) {
     BwdWork wk;
-    int entry = w / p.heads_k;
-    wk.head_k = w - entry * p.heads_k;
+    // Work order: key/value heads are taken `sg_heads` at a time ("supergroup"); inside a
+    // supergroup the entries run in list order (most expensive first) with the head minor.
+    // CTAs that run at the same time then add into the dQ tiles of few heads, which keeps the
+    // fp32 dQ accumulator they share resident in L2.  BSHD applies this per batch element.
+    const int entries = p.cu_seqlens_q == nullptr ? p.num_entries_host : *p.num_entries_dev;
+    int per_batch = entries, b_idx = 0;
+    if (p.cu_seqlens_q == nullptr && p.ring_docs == nullptr) {
+        per_batch = (p.seqlen_k + kTileN - 1) / kTileN;
+        b_idx = w / (per_batch * p.heads_k);
+        w -= b_idx * per_batch * p.heads_k;
+    }
+    const int per_sg = per_batch * p.sg_heads;
+    const int sg = w / per_sg;
+    const int sg_base = sg * p.sg_heads;
+    const int sg_cnt = min(p.sg_heads, p.heads_k - sg_base);
+    const int sg_r = w - sg * per_sg;
+    int entry = sg_r / sg_cnt;
+    wk.head_k = sg_base + (sg_r - entry * sg_cnt);
+    entry += b_idx * per_batch;
     wk.first1 = 0;
     wk.count1 = 0;
     wk.seg_len = 0;
@@ -211,7 +232,8 @@ struct __align__(1024) BwdShared {
     uint8_t k[kTileBytes];
     uint8_t v[kTileBytes];
     uint8_t q[kBwdStages][kTileBytes];
-    uint8_t dout[kBwdStages][kTileBytes];
+    uint8_t dout[kDoStages][kTileBytes];
+    uint8_t dq_stage[2][kDqChunkBytes];   // dQ chunks on their way to the bulk reduce-add
     uint8_t ds[kTileBytes];
     float lse2[kBwdStages][kTileM];
     float dpsum[kBwdStages][kTileM];
@@ -219,8 +241,8 @@ struct __align__(1024) BwdShared {
     uint64_t kv_empty;
     uint64_t q_full[kBwdStages];
     uint64_t q_empty[kBwdStages];
-    uint64_t do_full[kBwdStages];
-    uint64_t do_empty[kBwdStages];
+    uint64_t do_full[kDoStages];
+    uint64_t do_empty[kDoStages];
     uint64_t s_full;
     uint64_t dp_full;
     uint64_t p_ready;
@@ -241,7 +263,7 @@ struct __align__(1024) BwdShared {
 static_assert(sizeof(BwdShared) <= 232448, "backward shared storage exceeds the 227 KiB opt-in limit");
 
 // Copy role of a ring-mode backward CTA (same protocol as the forward's): six 32 KiB slots laid
-// over the K ... dO tile buffers, one loading thread, one storing thread, per-block ready flags.
+// over the K ... dO tile buffers and the dQ staging area, one loading thread, one storing thread, per-block ready flags.
 __device__ __forceinline__ void bwd_ring_copy_role(const BwdParams& p, BwdShared& sh, const WaitCtx& wctx,
                                                    int warp, int lane) {
     constexpr uint32_t kSlotBytes = kTileBytes;
@@ -322,6 +344,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         for (int i = 0; i < kBwdStages; ++i) {
             mbar_init(smem_u32(&sh.q_full[i]), 1);
             mbar_init(smem_u32(&sh.q_empty[i]), 1);
+        }
+        for (int i = 0; i < kDoStages; ++i) {
             mbar_init(smem_u32(&sh.do_full[i]), 1);
             mbar_init(smem_u32(&sh.do_empty[i]), 1);
         }
@@ -368,7 +392,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     }
 
     if (warp >= 12) {
-        reg_dealloc<88>();
+        reg_dealloc<80>();
         if (warp == 13) {
             // ------------------------------------------------------------ load warp
             if (lane == 0) {
@@ -420,6 +444,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     const int q_local = bwd_step_row(wk, t % per_head, &diag);
                     const uint32_t stage = step_it % kBwdStages;
                     const uint32_t par = ((step_it / kBwdStages) & 1u) ^ 1u;
+                    const uint32_t do_stage = step_it % kDoStages;
+                    const uint32_t do_par = ((step_it / kDoStages) & 1u) ^ 1u;
                     ++step_it;
                     ok = mbar_wait(wctx, smem_u32(&sh.q_empty[stage]), par, 3);
                     if (!ok) break;
@@ -435,11 +461,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                         bulk_load_1d(smem_u32(&sh.lse2[stage][0]), p.lse2 + vec, kRowVecBytes, bar);
                         bulk_load_1d(smem_u32(&sh.dpsum[stage][0]), p.dpsum + vec, kRowVecBytes, bar);
                     }
-                    ok = mbar_wait(wctx, smem_u32(&sh.do_empty[stage]), par, 4);
+                    ok = mbar_wait(wctx, smem_u32(&sh.do_empty[do_stage]), do_par, 4);
                     if (!ok) break;
                     if (lane == 0) {
-                        const uint32_t bar = smem_u32(&sh.do_full[stage]);
-                        const uint32_t dst = smem_u32(&sh.dout[stage][0]);
+                        const uint32_t bar = smem_u32(&sh.do_full[do_stage]);
+                        const uint32_t dst = smem_u32(&sh.dout[do_stage][0]);
                         const int row = wk.q_begin + q_local;
                         mbar_arrive_expect_tx(bar, kTileBytes);
                         tma_load_3d(dst, &map_do, bar, 0, hq, row);
@@ -452,18 +478,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);   // K-major A, K-major B
             constexpr uint32_t idesc_kn = make_idesc_bf16(128, 128, 0, 1);   // K-major A, MN-major B
             constexpr uint32_t idesc_nn = make_idesc_bf16(128, 128, 1, 1);   // MN-major A, MN-major B
-            const uint32_t k_addr = smem_u32(&sh.k[0]);
-            const uint32_t v_addr = smem_u32(&sh.v[0]);
-            const uint32_t ds_addr = smem_u32(&sh.ds[0]);
+            // Descriptor low words (see desc_lo_kmajor): K, V, dS^T tiles and stage 0 of Q / dO.
+            const uint32_t k_lo_k = desc_lo_kmajor(smem_u32(&sh.k[0]));
+            const uint32_t k_lo_n = desc_lo_mnmajor(smem_u32(&sh.k[0]));
+            const uint32_t v_lo_k = desc_lo_kmajor(smem_u32(&sh.v[0]));
+            const uint32_t ds_lo_k = desc_lo_kmajor(smem_u32(&sh.ds[0]));
+            const uint32_t ds_lo_n = desc_lo_mnmajor(smem_u32(&sh.ds[0]));
+            const uint32_t q_lo_k0 = desc_lo_kmajor(smem_u32(&sh.q[0][0]));
+            const uint32_t q_lo_n0 = desc_lo_mnmajor(smem_u32(&sh.q[0][0]));
+            const uint32_t do_lo_k0 = desc_lo_kmajor(smem_u32(&sh.dout[0][0]));
+            const uint32_t do_lo_n0 = desc_lo_mnmajor(smem_u32(&sh.dout[0][0]));
+            constexpr uint32_t kStageStep = kTileBytes >> 4;
 
             // D[128 x 128] = A * B^T with both operands K-major [rows][128] tiles.
-            auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr) {
+            auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
-                    umma_ss(d_tmem, make_smem_desc_sw128(a_addr + off, 16, 1024),
-                            make_smem_desc_sw128(b_addr + off, 16, 1024), idesc_kk,
-                            ks > 0 ? 1u : 0u);
+                    umma_ss_lo(d_tmem, a_lo + kstep_kmajor(ks), b_lo + kstep_kmajor(ks), idesc_kk,
+                               ks > 0 ? 1u : 0u);
                 }
             };
 
@@ -471,6 +503,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             uint32_t step_it = 0;
             uint32_t p_cnt = 0, ds_cnt = 0, drain_cnt = 0;
             bool ok = true;
+            PH_DECL(8)   // 0 other, 1 wait p_ready, 2 issue dV/S, 3 wait ds_ready, 4 issue dQ/dK, 5 wait drained, 6 wait dO + issue dP
             for (uint32_t it = 0; ok; ++it) {
                 const uint32_t slot = it & 1u;
                 ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 5);
@@ -495,15 +528,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     if (!ok) break;
                     tc_fence_after_sync();
                     if (lane == 0) {
-                        issue_kmajor(tmem_base + kColS, k_addr, smem_u32(&sh.q[stage][0]));
+                        issue_kmajor(tmem_base + kColS, k_lo_k, q_lo_k0 + stage * kStageStep);
                         tc_commit(smem_u32(&sh.s_full));
                     }
                     __syncwarp();
-                    ok = mbar_wait(wctx, smem_u32(&sh.do_full[stage]), par, 9);
+                    const uint32_t do_stage = step_it % kDoStages;
+                    ok = mbar_wait(wctx, smem_u32(&sh.do_full[do_stage]), (step_it / kDoStages) & 1u, 9);
                     if (!ok) break;
                     tc_fence_after_sync();
                     if (lane == 0) {
-                        issue_kmajor(tmem_base + kColDP, v_addr, smem_u32(&sh.dout[stage][0]));
+                        issue_kmajor(tmem_base + kColDP, v_lo_k, do_lo_k0 + do_stage * kStageStep);
                         tc_commit(smem_u32(&sh.dp_full));
                     }
                     __syncwarp();
@@ -512,15 +546,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     const uint32_t stage = step_it % kBwdStages;
                     const uint32_t nstage = (step_it + 1) % kBwdStages;
                     const uint32_t npar = ((step_it + 1) / kBwdStages) & 1u;
+                    const uint32_t do_stage = step_it % kDoStages;
+                    const uint32_t do_nstage = (step_it + 1) % kDoStages;
+                    const uint32_t do_npar = ((step_it + 1) / kDoStages) & 1u;
                     ++step_it;
-                    const uint32_t q_addr = smem_u32(&sh.q[stage][0]);
-                    const uint32_t do_addr = smem_u32(&sh.dout[stage][0]);
+                    const uint32_t q_lo_n = q_lo_n0 + stage * kStageStep;
+                    const uint32_t do_lo_n = do_lo_n0 + do_stage * kStageStep;
                     const bool has_next = t + 1 < steps;
 
                     // dV += P^T dO   (A = P^T from tensor memory, B = dO as MN-major)
+                    PH_MARK(0);
                     ok = mbar_wait(wctx, smem_u32(&sh.p_ready), p_cnt & 1u, 10);
                     if (!ok) break;
                     ++p_cnt;
+                    PH_MARK(1);
                     if (t == 0) {
                         // dK/dV accumulators must have been read out by the previous item's
                         // epilogue before they are overwritten.
@@ -532,45 +571,47 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
                             const uint32_t a_col = kColS + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
-                            umma_ts(tmem_base + kColDV, tmem_base + a_col,
-                                    make_smem_desc_sw128(do_addr + ks * 2048, kHalfTileBytes, 1024),
-                                    idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
+                            umma_ts_lo(tmem_base + kColDV, tmem_base + a_col, do_lo_n + kstep_mnmajor(ks),
+                                       idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
                         }
-                        tc_commit(smem_u32(&sh.do_empty[stage]));
+                        tc_commit(smem_u32(&sh.do_empty[do_stage]));
                     }
                     __syncwarp();
+                    PH_MARK(7);
+#ifdef B2A_PHASES
+                    ph_[9] += 1;
+#endif
                     // S^T(t+1) = K Q(t+1)^T
                     if (has_next) {
                         ok = mbar_wait(wctx, smem_u32(&sh.q_full[nstage]), npar, 11);
                         if (!ok) break;
+                        PH_MARK(8);
                         tc_fence_after_sync();
                         if (lane == 0) {
-                            issue_kmajor(tmem_base + kColS, k_addr, smem_u32(&sh.q[nstage][0]));
+                            issue_kmajor(tmem_base + kColS, k_lo_k, q_lo_k0 + nstage * kStageStep);
                             tc_commit(smem_u32(&sh.s_full));
                         }
                         __syncwarp();
                     }
                     // dQ(t) = dS K  (A = dS^T tile read MN-major, B = K as MN-major), then
                     // dK += dS^T Q  (A = dS^T tile read K-major, B = Q as MN-major)
+                    PH_MARK(2);
                     ok = mbar_wait(wctx, smem_u32(&sh.ds_ready), ds_cnt & 1u, 12);
                     if (!ok) break;
                     ++ds_cnt;
+                    PH_MARK(3);
                     tc_fence_after_sync();
                     if (lane == 0) {
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
-                            umma_ss(tmem_base + kColDP,
-                                    make_smem_desc_sw128(ds_addr + ks * 2048, kHalfTileBytes, 1024),
-                                    make_smem_desc_sw128(k_addr + ks * 2048, kHalfTileBytes, 1024),
-                                    idesc_nn, ks > 0 ? 1u : 0u);
+                            umma_ss_lo(tmem_base + kColDP, ds_lo_n + kstep_mnmajor(ks), k_lo_n + kstep_mnmajor(ks),
+                                       idesc_nn, ks > 0 ? 1u : 0u);
                         }
                         tc_commit(smem_u32(&sh.dq_full));
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
-                            const uint32_t off = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
-                            umma_ss(tmem_base + kColDK, make_smem_desc_sw128(ds_addr + off, 16, 1024),
-                                    make_smem_desc_sw128(q_addr + ks * 2048, kHalfTileBytes, 1024),
-                                    idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
+                            umma_ss_lo(tmem_base + kColDK, ds_lo_k + kstep_kmajor(ks), q_lo_n + kstep_mnmajor(ks),
+                                       idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
                         }
                         tc_commit(smem_u32(&sh.q_empty[stage]));
                         tc_commit(smem_u32(&sh.ds_empty));
@@ -581,30 +622,35 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     }
                     __syncwarp();
                     // dP^T(t+1) = V dO(t+1)^T, once dQ(t) has left tensor memory.
+                    PH_MARK(4);
                     ok = mbar_wait(wctx, smem_u32(&sh.dq_drained), drain_cnt & 1u, 13);
                     if (!ok) break;
                     ++drain_cnt;
+                    PH_MARK(5);
                     if (has_next) {
-                        ok = mbar_wait(wctx, smem_u32(&sh.do_full[nstage]), npar, 14);
+                        ok = mbar_wait(wctx, smem_u32(&sh.do_full[do_nstage]), do_npar, 14);
                         if (!ok) break;
                         tc_fence_after_sync();
                         if (lane == 0) {
-                            issue_kmajor(tmem_base + kColDP, v_addr, smem_u32(&sh.dout[nstage][0]));
+                            issue_kmajor(tmem_base + kColDP, v_lo_k, do_lo_k0 + do_nstage * kStageStep);
                             tc_commit(smem_u32(&sh.dp_full));
                         }
                         __syncwarp();
                     }
+                    PH_MARK(6);
                 }
             }
+            PH_PRINT("mma", 7);
         }
     } else if (warp >= 8) {
         // -------------------------------------------------------------------- dQ warpgroup
-        reg_dealloc<72>();
+        reg_alloc<144>();
         const int r = (warp & 3) * 32 + lane;   // query row within the tile
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t dq_tmem = tmem_base + lane_base + kColDP;
         uint32_t dq_cnt = 0;
         bool ok = true;
+        PH_DECL(4)   // 0 other, 1 wait dq_full, 2 load + arrive, 3 reductions
         for (uint32_t it = 0; ok; ++it) {
             const uint32_t slot = it & 1u;
             ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 15);
@@ -624,36 +670,53 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 float* tile = p.dq_accum +
                               (static_cast<long long>(hq) * pad_tiles + (wk.q_pad_begin + q_local) / kTileM) *
                                   kDqTileFloats;
+                PH_MARK(0);
                 ok = mbar_wait(wctx, smem_u32(&sh.dq_full), dq_cnt & 1u, 16);
                 if (!ok) break;
                 ++dq_cnt;
                 tc_fence_after_sync();
+                PH_MARK(1);
+                // Pull the whole dQ tile into registers first so that tensor memory is handed back
+                // before the reductions are issued.
+                uint32_t v[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld_x32(dq_tmem + c * 32, v[c]);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&sh.dq_drained));
+                PH_MARK(2);
+                // Four chunks of 32 columns go through two 16 KiB staging buffers whose layout
+                // equals the accumulator's ([8 column quads][128 rows][4 floats]); one thread hands
+                // each to the bulk-copy engine as an fp32 reduce-add into global memory, so the
+                // additions run asynchronously and do not occupy this SM's load/store path.
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_x32(dq_tmem + c * 32, v);
-                    tmem_wait_ld();
-                    if (c == 3) {
-                        // All of dQ(t) is in registers: tensor memory may be overwritten.
-                        tc_fence_before_sync();
-                        mbar_arrive(smem_u32(&sh.dq_drained));
-                    }
+                    const uint32_t buf = smem_u32(&sh.dq_stage[c & 1][0]);
+                    if (threadIdx.x == 256) bulk_wait_group_read<1>();   // the buffer's previous reduction has read it
+                    named_barrier_sync(kDqBarrier, 128);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        float* dst = tile + ((c * 8 + i) * kTileM + r) * 4;
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
-                                     ::"l"(dst), "f"(__uint_as_float(v[4 * i])),
-                                       "f"(__uint_as_float(v[4 * i + 1])),
-                                       "f"(__uint_as_float(v[4 * i + 2])),
-                                       "f"(__uint_as_float(v[4 * i + 3]))
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(buf + static_cast<uint32_t>((i * kTileM + r) * 16)),
+                                       "r"(v[c][4 * i]), "r"(v[c][4 * i + 1]), "r"(v[c][4 * i + 2]),
+                                       "r"(v[c][4 * i + 3])
                                      : "memory");
                     }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(kDqBarrier, 128);
+                    if (threadIdx.x == 256) {
+                        bulk_reduce_add_f32(tile + c * (kDqChunkBytes / 4), buf, kDqChunkBytes);
+                        bulk_commit_group();
+                    }
                 }
+                PH_MARK(3);
             }
         }
+        if (threadIdx.x == 256) bulk_wait_group<0>();   // all reductions performed before the CTA ends
+        PH_PRINT("dq", 4);
     } else {
         // -------------------------------------------------------------------- compute warpgroups
-        reg_alloc<176>();
+        reg_alloc<144>();
         const int wg = warp >> 2;                      // 0: query columns 0-63, 1: 64-127
         const int i_row = (warp & 3) * 32 + lane;      // key row within the block
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -665,6 +728,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         uint32_t step_it = 0;
         uint32_t s_cnt = 0, dp_cnt = 0, dse_cnt = 0, epi_cnt = 0;
         bool ok = true;
+        PH_DECL(8)   // 0 other, 1 wait q_full+s_full, 2 P phase, 3 wait dp_full, 4 dP load, 5 wait ds_empty, 6 dS phase
 
         for (uint32_t it = 0; ok; ++it) {
             const uint32_t slot = it & 1u;
@@ -696,12 +760,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 const bool need_mask = !kv_valid || c_min > 0;
 
                 // LSE2 / D of this tile arrive with Q.
+                PH_MARK(0);
                 ok = mbar_wait(wctx, smem_u32(&sh.q_full[stage]), par, 18);
                 if (!ok) break;
                 ok = mbar_wait(wctx, smem_u32(&sh.s_full), s_cnt & 1u, 19);
                 if (!ok) break;
                 ++s_cnt;
                 tc_fence_after_sync();
+                PH_MARK(1);
 
                 float pr[64];
                 {
@@ -744,53 +810,54 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 }
 
                 // dS^T = P^T * (dP^T - D)
+                PH_MARK(2);
                 ok = mbar_wait(wctx, smem_u32(&sh.dp_full), dp_cnt & 1u, 20);
                 if (!ok) break;
                 ++dp_cnt;
                 tc_fence_after_sync();
-                uint32_t dsp[32];
-                {
-                    uint32_t a[32], b[32];
-                    tmem_ld_x32(dp_tmem, a);
-                    tmem_ld_x32(dp_tmem + 32, b);
-                    tmem_wait_ld();
-                    const float4* dsum = reinterpret_cast<const float4*>(&sh.dpsum[stage][wg * 64]);
-#pragma unroll
-                    for (int g4 = 0; g4 < 8; ++g4) {
-                        const float4 d = dsum[g4];
-                        const float x0 = pr[4 * g4 + 0] * (__uint_as_float(a[4 * g4 + 0]) - d.x);
-                        const float x1 = pr[4 * g4 + 1] * (__uint_as_float(a[4 * g4 + 1]) - d.y);
-                        const float x2 = pr[4 * g4 + 2] * (__uint_as_float(a[4 * g4 + 2]) - d.z);
-                        const float x3 = pr[4 * g4 + 3] * (__uint_as_float(a[4 * g4 + 3]) - d.w);
-                        dsp[2 * g4] = pack_bf16x2(x0, x1);
-                        dsp[2 * g4 + 1] = pack_bf16x2(x2, x3);
-                    }
-#pragma unroll
-                    for (int g4 = 0; g4 < 8; ++g4) {
-                        const float4 d = dsum[8 + g4];
-                        const float x0 = pr[32 + 4 * g4 + 0] * (__uint_as_float(b[4 * g4 + 0]) - d.x);
-                        const float x1 = pr[32 + 4 * g4 + 1] * (__uint_as_float(b[4 * g4 + 1]) - d.y);
-                        const float x2 = pr[32 + 4 * g4 + 2] * (__uint_as_float(b[4 * g4 + 2]) - d.z);
-                        const float x3 = pr[32 + 4 * g4 + 3] * (__uint_as_float(b[4 * g4 + 3]) - d.w);
-                        dsp[16 + 2 * g4] = pack_bf16x2(x0, x1);
-                        dsp[16 + 2 * g4 + 1] = pack_bf16x2(x2, x3);
-                    }
-                }
+                PH_MARK(3);
+                // Two halves of 32 query columns each keep the live register set small.
+                uint32_t a[32], b[32];
+                tmem_ld_x32(dp_tmem, a);
+                tmem_ld_x32(dp_tmem + 32, b);
+                const float4* dsum = reinterpret_cast<const float4*>(&sh.dpsum[stage][wg * 64]);
+                tmem_wait_ld();
+                PH_MARK(4);
                 // The previous step's dK / dQ MMAs must be done with the dS^T tile.
                 ok = mbar_wait(wctx, smem_u32(&sh.ds_empty), (dse_cnt & 1u) ^ 1u, 21);
                 if (!ok) break;
                 ++dse_cnt;
+                PH_MARK(5);
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    const uint32_t addr = ds_row + ((ch ^ (i_row & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(addr), "r"(dsp[4 * ch]), "r"(dsp[4 * ch + 1]),
-                                   "r"(dsp[4 * ch + 2]), "r"(dsp[4 * ch + 3])
-                                 : "memory");
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t dsp[16];
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        const float4 d = dsum[half * 8 + g4];
+                        const uint32_t* src = half == 0 ? a : b;
+                        const float x0 = pr[half * 32 + 4 * g4 + 0] * (__uint_as_float(src[4 * g4 + 0]) - d.x);
+                        const float x1 = pr[half * 32 + 4 * g4 + 1] * (__uint_as_float(src[4 * g4 + 1]) - d.y);
+                        const float x2 = pr[half * 32 + 4 * g4 + 2] * (__uint_as_float(src[4 * g4 + 2]) - d.z);
+                        const float x3 = pr[half * 32 + 4 * g4 + 3] * (__uint_as_float(src[4 * g4 + 3]) - d.w);
+                        dsp[2 * g4] = pack_bf16x2(x0, x1);
+                        dsp[2 * g4 + 1] = pack_bf16x2(x2, x3);
+                    }
+                    PH_MARK(6);
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const uint32_t addr = ds_row + (((half * 4 + ch) ^ (i_row & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(addr), "r"(dsp[4 * ch]), "r"(dsp[4 * ch + 1]),
+                                       "r"(dsp[4 * ch + 2]), "r"(dsp[4 * ch + 3])
+                                     : "memory");
+                    }
+                    PH_MARK(7);
                 }
                 fence_proxy_async_smem();
+                PH_MARK(8);
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&sh.ds_ready));
+                PH_MARK(9);
             }
             if (!ok) break;
 
@@ -850,6 +917,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 mbar_arrive(smem_u32(&sh.dkv_empty));
             }
         }
+        PH_PRINT("compute", 7);
     }
 
     if (p.ring_docs != nullptr) {

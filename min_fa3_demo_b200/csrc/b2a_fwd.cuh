@@ -464,30 +464,32 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             uint32_t q_cnt[2] = {0, 0};
             uint32_t p_cnt[2] = {0, 0};
             bool ok = true;
+            PH_DECL(8)   // 0 other, 1 wait p_full, 2 issue PV, 3 wait K, 4 issue S
             const uint32_t s_tmem[2] = {tmem_base + 0u, tmem_base + 128u};
             const uint32_t o_tmem[2] = {tmem_base + 256u, tmem_base + 384u};
 
+            // Descriptor low words of the Q tiles and of K/V stage 0 (a stage is 32 KiB further).
+            const uint32_t q_lo[2] = {desc_lo_kmajor(smem_u32(&sh.q[0][0])), desc_lo_kmajor(smem_u32(&sh.q[1][0]))};
+            const uint32_t k_lo0 = desc_lo_kmajor(smem_u32(&sh.kv[0][0]));
+            const uint32_t v_lo0 = desc_lo_mnmajor(smem_u32(&sh.kv[0][0]));
+            constexpr uint32_t kStageStep = kTileBytes >> 4;
+
             // S_x = Q_x * K^T for the K tile in `stage` (8 k-steps of 16 over head_dim).
             auto issue_qk = [&](int x, uint32_t stage) {
-                const uint32_t q_addr = smem_u32(&sh.q[x][0]);
-                const uint32_t k_addr = smem_u32(&sh.kv[stage][0]);
+                const uint32_t b0 = k_lo0 + stage * kStageStep;
 #pragma unroll
                 for (int ks = 0; ks < kHeadDim / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
-                    const uint64_t a = make_smem_desc_sw128(q_addr + off, 16, 1024);
-                    const uint64_t b = make_smem_desc_sw128(k_addr + off, 16, 1024);
-                    umma_ss(s_tmem[x], a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                    umma_ss_lo(s_tmem[x], q_lo[x] + kstep_kmajor(ks), b0 + kstep_kmajor(ks), idesc_qk,
+                               ks > 0 ? 1u : 0u);
                 }
             };
             // O_x (+)= P_x * V for the V tile in `stage` (8 k-steps of 16 over keys).
             auto issue_pv = [&](int x, uint32_t stage, uint32_t accumulate) {
-                const uint32_t v_addr = smem_u32(&sh.kv[stage][0]);
+                const uint32_t b0 = v_lo0 + stage * kStageStep;
 #pragma unroll
                 for (int ks = 0; ks < kTileN / 16; ++ks) {
-                    const uint64_t b =
-                        make_smem_desc_sw128(v_addr + ks * 2048, kHalfTileBytes, 1024);
-                    umma_ts(o_tmem[x], s_tmem[x] + ks * 8, b, idesc_pv,
-                            (ks > 0 || accumulate) ? 1u : 0u);
+                    umma_ts_lo(o_tmem[x], s_tmem[x] + ks * 8, b0 + kstep_mnmajor(ks), idesc_pv,
+                               (ks > 0 || accumulate) ? 1u : 0u);
                 }
             };
 
@@ -547,15 +549,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
                     for (int x = 0; x < 2; ++x) {
                         if (j < nblk[x]) {
+                            PH_MARK(0);
                             ok = mbar_wait(wctx, smem_u32(&sh.p_full[x]), p_cnt[x] & 1u, 8);
                             if (!ok) break;
                             ++p_cnt[x];
                             tc_fence_after_sync();
+                            PH_MARK(1);
                             if (lane == 0) {
                                 issue_pv(x, stage_v, j != nblk[x] - 1 ? 1u : 0u);
                                 if (j == 0) tc_commit(smem_u32(&sh.o_full[x]));
                             }
                             __syncwarp();
+                            PH_MARK(2);
+#ifdef B2A_PHASES
+                            ph_[9] += 1;
+#endif
                         }
                         if (x == 1 && lane == 0) {
                             tc_commit(smem_u32(&sh.kv_empty[stage_v]));
@@ -567,6 +575,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                                 if (!ok) break;
                                 tc_fence_after_sync();
                             }
+                            PH_MARK(3);
                             if (j - 1 < nblk[x] && lane == 0) {
                                 issue_qk(x, stage_k);
                                 tc_commit(smem_u32(&sh.s_full[x]));
@@ -576,11 +585,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                                 tc_commit(smem_u32(&sh.kv_empty[stage_k]));
                             }
                             __syncwarp();
+                            PH_MARK(4);
                         }
                     }
                     if (j > 0) ++kv_it;
                 }
             }
+            PH_PRINT("fwd mma", 5);
         }
     } else {
         // ---------------------------------------------------------------- softmax warpgroups
@@ -594,6 +605,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         uint32_t o_cnt = 0;
         bool ok = true;
         const float sl2 = p.scale_log2;
+        PH_DECL(8)   // 0 other, 1 wait s_full, 2 tmem load, 3 max/rescale, 4 exp + store, 5 st wait + arrive
 
         for (uint32_t it = 0; ok; ++it) {
             const uint32_t slot = it & 1u;
@@ -630,10 +642,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             float l = 0.f;              // running row sum relative to m_used
 
             for (int j = nblk - 1; j >= 0; --j) {
+                PH_MARK(0);
                 ok = mbar_wait(wctx, smem_u32(&sh.s_full[x]), s_cnt & 1u, 11);
                 if (!ok) break;
                 ++s_cnt;
                 tc_fence_after_sync();
+                PH_MARK(1);
 
                 float s[kTileN];
 #pragma unroll
@@ -644,6 +658,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(t[i]);
                 }
                 tmem_wait_ld();
+                PH_MARK(2);
 
                 const int n0 = (j - wk.n_full) * kTileN;   // own-chunk column of the block
                 if (j >= wk.n_full && n0 + kTileN > tile_min_limit) {
@@ -654,9 +669,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     }
                 }
 
-                float bm = s[0];
+                // Row maximum with four independent chains of 3-input maxima (a single chain of
+                // 127 dependent operations would be pure latency for the one warp per scheduler).
+                float bm;
+                {
+                    float m0 = s[0], m1 = s[1], m2 = s[2], m3 = s[3];
 #pragma unroll
-                for (int i = 1; i < kTileN; ++i) bm = fmaxf(bm, s[i]);
+                    for (int i = 4; i + 7 < kTileN; i += 8) {
+                        m0 = max3(m0, s[i], s[i + 1]);
+                        m1 = max3(m1, s[i + 2], s[i + 3]);
+                        m2 = max3(m2, s[i + 4], s[i + 5]);
+                        m3 = max3(m3, s[i + 6], s[i + 7]);
+                    }
+                    // 4 + 15 * 8 = 124 consumed; four left
+                    m0 = max3(m0, s[124], s[125]);
+                    m1 = max3(m1, s[126], s[127]);
+                    bm = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+                }
 
                 const bool first = (j == nblk - 1);
                 const float m_new = fmaxf(m_used, bm);
@@ -683,24 +712,33 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     }
                 }
 
+                PH_MARK(3);
                 const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used * sl2;
-                float sum = 0.f;
+                const float2 sl2v = make_float2(sl2, sl2);
+                const float2 negv = make_float2(neg_m, neg_m);
+                float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     uint32_t t[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float p0 = fast_exp2(fmaf(s[c * 64 + 2 * i], sl2, neg_m));
-                        const float p1 = fast_exp2(fmaf(s[c * 64 + 2 * i + 1], sl2, neg_m));
-                        sum += p0 + p1;
-                        t[i] = pack_bf16x2(p0, p1);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float2 x0 = fma2(make_float2(s[c * 64 + 2 * i], s[c * 64 + 2 * i + 1]), sl2v, negv);
+                        const float2 x1 = fma2(make_float2(s[c * 64 + 2 * i + 2], s[c * 64 + 2 * i + 3]), sl2v, negv);
+                        const float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
+                        const float2 p1 = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
+                        acc0 = add2(acc0, p0);
+                        acc1 = add2(acc1, p1);
+                        t[i] = pack_bf16x2(p0.x, p0.y);
+                        t[i + 1] = pack_bf16x2(p1.x, p1.y);
                     }
                     tmem_st_x32(s_tmem + c * 32, t);
                 }
-                l += sum;
+                l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+                PH_MARK(4);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&sh.p_full[x]));
+                PH_MARK(5);
             }
             if (!ok) break;
 
@@ -793,6 +831,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             }
             tc_fence_before_sync();
         }
+        PH_PRINT("fwd softmax", 6);
     }
 
     // Common exit: every role arrives here (normally or after an abort).

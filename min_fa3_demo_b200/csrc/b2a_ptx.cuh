@@ -10,6 +10,21 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+// Optional phase timing (compile with -DB2A_PHASES): per-role cycle accumulators printed by
+// CTA 0 at kernel exit.  Compiled out by default.
+#ifdef B2A_PHASES
+#include <cstdio>
+#define PH_DECL(n) long long ph_[10] = {0}; long long ph_t_ = clock64();
+#define PH_MARK(i) do { long long now_ = clock64(); ph_[i] += now_ - ph_t_; ph_t_ = now_; } while (0)
+#define PH_PRINT(name, n) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { \
+    printf("[phases] %s warp %d: %lld %lld %lld %lld %lld %lld %lld %lld %lld %lld\n", name, (int)(threadIdx.x >> 5), \
+           ph_[0], ph_[1], ph_[2], ph_[3], ph_[4], ph_[5], ph_[6], ph_[7], ph_[8], ph_[9]); } } while (0)
+#else
+#define PH_DECL(n)
+#define PH_MARK(i)
+#define PH_PRINT(name, n)
+#endif
+
 namespace b2a {
 
 // ----------------------------------------------------------------------------
@@ -305,6 +320,59 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         : "memory");
 }
 
+// Split form of the 128-byte-swizzle descriptor for the issue loops: the high word is a
+// constant (stride offset 1024 B, version 1, layout 2) and the low word is
+// (address >> 4) | (leading offset >> 4) << 16, so stepping through a tile is one 32-bit add
+// per operand.  (A single issuing thread has little instruction-level parallelism: building
+// full 64-bit descriptors per MMA costs more than the 64 cycles the MMA itself takes.)
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t smem_addr) {
+    return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+}
+
+// MN-major operand made of two 64-column halves 16 KiB apart.
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t smem_addr) {
+    return ((smem_addr & 0x3FFFFu) >> 4) | ((16384u >> 4) << 16);
+}
+
+// Low-word increment of k-step `ks` (16 elements) inside a [128 rows][128 columns] tile.
+__host__ __device__ constexpr uint32_t kstep_kmajor(int ks) {
+    return static_cast<uint32_t>((ks >> 2) * (16384 >> 4) + (ks & 3) * (32 >> 4));
+}
+__host__ __device__ constexpr uint32_t kstep_mnmajor(int ks) {
+    return static_cast<uint32_t>(ks * (2048 >> 4));
+}
+
+__device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
 // ----------------------------------------------------------------------------
 // tcgen05: TMEM <-> registers.  Shape 32x32b: thread t of the warp addresses
 // TMEM lane (lane_base + t); xN moves N consecutive 32-bit columns.
@@ -360,6 +428,43 @@ __device__ __forceinline__ float fast_log2(float x) {
     float y;
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Packed fp32x2 arithmetic (two lanes per instruction on sm_100): halves the issue slots of
+// the scale/subtract and row-sum steps of the softmax.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "mov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}\n"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}\n"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
