@@ -28,6 +28,14 @@
 namespace b2a {
 
 constexpr int kBwdThreads = 512;
+// Which of the 16 four-element groups of a thread's 64 probabilities take two of their
+// exponentials from the FMA-pipe polynomial instead of the special-function unit.  Off by
+// default: measured in SM clocks per step, 0 / 25 % / 50 % polynomial gave 3990 / 4090 / 4280
+// (the compute warps of this kernel are short of issue slots, not of special-function rate).
+#ifndef B2A_BWD_EXP_POLY_MASK
+#define B2A_BWD_EXP_POLY_MASK 0x0000u
+#endif
+constexpr uint32_t kBwdExpPolyMask = B2A_BWD_EXP_POLY_MASK;
 constexpr int kBwdStages = 2;          // Q ring stages (with their LSE2 / D vectors)
 constexpr int kDoStages = 1;           // dO is single-buffered: it lives only from dP(t) to dV(t)
 constexpr uint32_t kDqBarrier = 1;          // named barrier of the dQ warpgroup
@@ -777,20 +785,23 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     tmem_wait_ld();
                     const float4* l2 = reinterpret_cast<const float4*>(&sh.lse2[stage][wg * 64]);
 #pragma unroll
-                    for (int g4 = 0; g4 < 8; ++g4) {
+                    for (int g4 = 0; g4 < 16; ++g4) {
                         const float4 l = l2[g4];
-                        pr[4 * g4 + 0] = fast_exp2(fmaf(__uint_as_float(a[4 * g4 + 0]), sl2, -l.x));
-                        pr[4 * g4 + 1] = fast_exp2(fmaf(__uint_as_float(a[4 * g4 + 1]), sl2, -l.y));
-                        pr[4 * g4 + 2] = fast_exp2(fmaf(__uint_as_float(a[4 * g4 + 2]), sl2, -l.z));
-                        pr[4 * g4 + 3] = fast_exp2(fmaf(__uint_as_float(a[4 * g4 + 3]), sl2, -l.w));
-                    }
-#pragma unroll
-                    for (int g4 = 0; g4 < 8; ++g4) {
-                        const float4 l = l2[8 + g4];
-                        pr[32 + 4 * g4 + 0] = fast_exp2(fmaf(__uint_as_float(b[4 * g4 + 0]), sl2, -l.x));
-                        pr[32 + 4 * g4 + 1] = fast_exp2(fmaf(__uint_as_float(b[4 * g4 + 1]), sl2, -l.y));
-                        pr[32 + 4 * g4 + 2] = fast_exp2(fmaf(__uint_as_float(b[4 * g4 + 2]), sl2, -l.z));
-                        pr[32 + 4 * g4 + 3] = fast_exp2(fmaf(__uint_as_float(b[4 * g4 + 3]), sl2, -l.w));
+                        const uint32_t* src = g4 < 8 ? a : b;
+                        const int o = (g4 & 7) * 4;
+                        const float2 x0 = fma2(make_float2(__uint_as_float(src[o]), __uint_as_float(src[o + 1])),
+                                               make_float2(sl2, sl2), make_float2(-l.x, -l.y));
+                        const float2 x1 = fma2(make_float2(__uint_as_float(src[o + 2]), __uint_as_float(src[o + 3])),
+                                               make_float2(sl2, sl2), make_float2(-l.z, -l.w));
+                        // Part of the exponentials runs as a polynomial on the FMA pipe (see exp2_poly2).
+                        const float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
+                        const float2 p1 = ((kBwdExpPolyMask >> g4) & 1u)
+                                              ? exp2_poly2(x1)
+                                              : make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
+                        pr[4 * g4 + 0] = p0.x;
+                        pr[4 * g4 + 1] = p0.y;
+                        pr[4 * g4 + 2] = p1.x;
+                        pr[4 * g4 + 3] = p1.y;
                     }
                 }
                 if (need_mask) {

@@ -510,6 +510,29 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
     return d;
 }
 
+// 2^x for two values on the FMA pipe instead of the special-function unit (16 ex2 per clock
+// per SM, which a 128x128 score tile keeps busy exactly as long as its two MMAs keep the tensor
+// pipe busy).  x = n + f with n = round(x) taken from the low mantissa bits of x + 1.5*2^23 and
+// f in [-0.5, 0.5]; 2^f by a degree-3 minimax polynomial (relative error 7.5e-5, far below the
+// bf16 rounding of the probabilities it feeds); n is then added into the exponent field.
+// Inputs below -126 (including -inf) give 2^-126, which rounds away in every later sum.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    constexpr float kMagic = 12582912.f;
+    x.x = fmaxf(x.x, -126.f);
+    x.y = fmaxf(x.y, -126.f);
+    const float2 t = add2(x, make_float2(kMagic, kMagic));
+    const float2 n = add2(t, make_float2(-kMagic, -kMagic));
+    const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
+    float2 p = fma2(f, make_float2(0.0551716648042202f, 0.0551716648042202f),
+                    make_float2(0.2426111400127411f, 0.2426111400127411f));
+    p = fma2(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+    p = fma2(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+    float2 r;
+    r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+    r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+    return r;
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
