@@ -410,5 +410,14 @@ def backward_varlen(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: tor
 # re-exported here so that this module carries the whole reference API surface.
 from .parallel import (TKParallelTensor, _resolve_parallel_context, create_parallel_tensor,  # noqa: E402,F401
                        parallel_remote_load, parallel_remote_load_vec)
-from .ring import (backward_varlen_mega_ring, forward_varlen_mega_ring,  # noqa: E402,F401
-                   forward_varlen_ring)
+
+_RING_EXPORTS = ("backward_varlen_mega_ring", "forward_varlen_mega_ring", "forward_varlen_ring")
+
+
+def __getattr__(name: str):
+    # The ring module imports helpers from this one, so its entry points are resolved on first
+    # use (either module may be imported first).
+    if name in _RING_EXPORTS:
+        from . import ring
+        return getattr(ring, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
