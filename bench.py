@@ -376,15 +376,46 @@ def run_ring_workload(args) -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    total, qh, kvh = args.ring_tokens, 32, 8
-    local = total // world
+    from min_fa3_demo_b200 import balancer as bal
+
+    varlen = args.workload == "ring_varlen"
+    if varlen:
+        # Config 5: mixture-distributed documents, load-balanced placement on sub-rings.
+        qh, kvh = 64, 8
+        lengths = bal.sample_mixture_lengths(0, target_tokens=args.ring_tokens)
+        lengths[-1] -= sum(lengths) - args.ring_tokens      # last document truncated to fill
+        if world > 1:
+            plan = bal.assign_hierarchical_rings(lengths, world, True)
+            glens, sizes, starts = plan.global_lengths, plan.ring_sizes, plan.ring_starts
+            lens, cu_list = bal.local_layout(plan, rank)
+            cap = max(sum(bal.local_layout(plan, r)[0]) for r in range(world))
+            balance = {"compute_deviation": plan.compute_deviation, "token_deviation": plan.token_deviation,
+                       "feasible": plan.feasible, "ring_sizes": sorted(set(sizes), reverse=True)}
+        else:
+            glens, sizes, starts = list(lengths), [1] * len(lengths), [0] * len(lengths)
+            lens = list(lengths)
+            cu_list = [0]
+            for n in lens:
+                cu_list.append(cu_list[-1] + n)
+            cap, balance = cu_list[-1], None
+    else:
+        # Config 4: one sequence over all ranks.
+        qh, kvh = 32, 8
+        glens, sizes, starts = [args.ring_tokens], [world], [0]
+        lens = [args.ring_tokens // world]
+        cu_list = [0, lens[0]]
+        cap, balance = lens[0], None
+    total = sum(glens)
+    cap = ((cap + 127) // 128) * 128
+    local = cu_list[-1]
+    max_len = max(lens)
     sm = torch.cuda.get_device_properties(dev).multi_processor_count
     gen = torch.Generator(device=dev).manual_seed(1000 + rank)
     q = torch.randn(local, qh, 128, device=dev, generator=gen).to(torch.bfloat16)
     k = torch.randn(local, kvh, 128, device=dev, generator=gen).to(torch.bfloat16)
     v = torch.randn(local, kvh, 128, device=dev, generator=gen).to(torch.bfloat16)
     dout = torch.randn(local, qh, 128, device=dev, generator=gen).to(torch.bfloat16)
-    cu = torch.tensor([0, local], dtype=torch.int32)
+    cu = torch.tensor(cu_list, dtype=torch.int32)
     cud = cu.to(dev)
 
     def barrier():
@@ -394,37 +425,38 @@ def run_ring_workload(args) -> None:
 
     if world == 1:
         def fwd():
-            return min_fa3_op.forward_varlen(q, k, v, cud, cud, local, local, True, cu_seqlens_q_host=cu,
+            return min_fa3_op.forward_varlen(q, k, v, cud, cud, max_len, max_len, True, cu_seqlens_q_host=cu,
                                              cu_seqlens_k_host=cu, return_lse=True)
 
         def bwd(out, lse):
-            return min_fa3_op.backward_varlen(dout, q, k, v, out, lse, cud, cud, local, local, True)
+            return min_fa3_op.backward_varlen(dout, q, k, v, out, lse, cud, cud, max_len, max_len, True)
 
         def reset():
             pass
     else:
-        arena_k = torch.zeros(world * local, kvh, 128, dtype=torch.bfloat16, device=dev)
+        arena_k = torch.zeros(world * cap, kvh, 128, dtype=torch.bfloat16, device=dev)
         arena_v = torch.zeros_like(arena_k)
-        arena_k[rank * local:(rank + 1) * local] = k
-        arena_v[rank * local:(rank + 1) * local] = v
+        arena_k[rank * cap:rank * cap + local] = k
+        arena_v[rank * cap:rank * cap + local] = v
         rk = min_fa3_op.TKParallelTensor(arena_k, local_rank=local_rank, local_world_size=world, multicast=False)
         rv = min_fa3_op.TKParallelTensor(arena_v, local_rank=local_rank, local_world_size=world, multicast=False)
-        acc_k = min_fa3_op.TKParallelTensor([kvh * local * 128], torch.float32, local_rank, world, False)
-        acc_v = min_fa3_op.TKParallelTensor([kvh * local * 128], torch.float32, local_rank, world, False)
+        acc_k = min_fa3_op.TKParallelTensor([kvh * cap * 128], torch.float32, local_rank, world, False)
+        acc_v = min_fa3_op.TKParallelTensor([kvh * cap * 128], torch.float32, local_rank, world, False)
         done = min_fa3_op.TKParallelTensor([1], torch.int32, local_rank, world, False)
-        meta = dict(global_seqlens_host=torch.tensor([total], dtype=torch.int32),
-                    ring_sizes_host=torch.tensor([world], dtype=torch.int32),
-                    ring_starts_host=torch.tensor([0], dtype=torch.int32))
+        meta = dict(global_seqlens_host=torch.tensor(glens, dtype=torch.int32),
+                    ring_sizes_host=torch.tensor(sizes, dtype=torch.int32),
+                    ring_starts_host=torch.tensor(starts, dtype=torch.int32))
         comm = args.ring_comm_sm
 
         def fwd():
             return min_fa3_op.forward_varlen_mega_ring(
-                q, rk.data_, rv.data_, cud, cud, local, local, True, cu_seqlens_q_host=cu, cu_seqlens_k_host=cu,
-                remote_k=rk, remote_v=rv, num_comp_sm=sm - comm, num_comm_sm=comm, return_lse=True, **meta)
+                q, rk.data_, rv.data_, cud, cud, max_len, max_len, True, cu_seqlens_q_host=cu,
+                cu_seqlens_k_host=cu, remote_k=rk, remote_v=rv, num_comp_sm=sm - comm, num_comm_sm=comm,
+                return_lse=True, **meta)
 
         def bwd(out, lse):
             return min_fa3_op.backward_varlen_mega_ring(
-                dout, q, rk.data_, rv.data_, out, lse, cud, cud, local, local, cu_seqlens_q_host=cu,
+                dout, q, rk.data_, rv.data_, out, lse, cud, cud, max_len, max_len, cu_seqlens_q_host=cu,
                 cu_seqlens_k_host=cu, remote_k=rk, remote_v=rv, remote_dk_accum=acc_k, remote_dv_accum=acc_v,
                 remote_dkv_completion=done, num_comp_sm=sm - comm, num_comm_sm=comm, **meta)
 
@@ -461,20 +493,26 @@ def run_ring_workload(args) -> None:
     sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
-        vis = total * (total + 1) / 2
+        vis = sum(n * (n + 1) / 2 for n in glens)
         f_flops, b_flops = 4.0 * qh * 128 * vis, 10.0 * qh * 128 * vis
         fm, bm = statistics.mean(fwd_ms), statistics.mean(bwd_ms)
         burst, sustained, peak_kind = measured_peaks()
         value = (f_flops + b_flops) / ((fm + bm) * 1e-3) / 1e12
-        # K/V bytes rank 0 pulls per forward: front halves of all other ranks (+ back halves of
-        # ranks after it): rank 0 pulls everything = (N-1) * local rows of K and V.
-        ingress = (world - 1) * local * kvh * 128 * 2 * 2
+        # K/V bytes rank 0 pulls per forward: for every document whose ring it is in, the shards of
+        # the other ring members (rank 0 holds the first and the last chunk of a zigzag ring, so it
+        # sees all of them).
+        ingress = sum((g - 1) * (n // g) for n, g, st in zip(glens, sizes, starts) if st == 0 and g > 1)
+        ingress *= kvh * 128 * 2 * 2
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": fm + bm, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"ring_cp_causal_S{total}_QH32_KVH8_D128", "tokens_per_gpu": local,
-                       "parallelism": f"cp{world} zigzag ring, K/V pulled over NVLink in-kernel"
+            "config": {"workload": (f"ring_varlen_cp_causal_T{total}_docs{len(glens)}_QH{qh}_KVH{kvh}_D128" if varlen
+                                    else f"ring_cp_causal_S{total}_QH{qh}_KVH{kvh}_D128"),
+                       "tokens_rank0": local, "documents": len(glens), "placement": balance,
+                       "parallelism": (f"cp{world} hierarchical zigzag sub-rings (load-balanced placement), "
+                                       "K/V pulled over NVLink in-kernel" if varlen else
+                                       f"cp{world} zigzag ring, K/V pulled over NVLink in-kernel")
                        if world > 1 else "single GPU (efficiency baseline)",
                        "copy_ctas": args.ring_comm_sm if world > 1 else 0,
                        "l2": "inputs larger than L2"},
@@ -493,6 +531,92 @@ def run_ring_workload(args) -> None:
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------
+# Packed varlen workload (BASELINE config 3)
+# --------------------------------------------------------------------------------------
+def varlen_lengths(total: int = 65536, seed: int = 0):
+    """Document lengths of config 3: log-normal (median 1,500, sigma 1.2) clipped to
+    [128, 32768], drawn until ``total`` tokens are reached, the last one truncated to fill."""
+    import math
+
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    out, acc = [], 0
+    while acc < total:
+        n = int(min(max(round(rng.lognormal(math.log(1500.0), 1.2)), 128), 32768))
+        n = min(n, total - acc)
+        out.append(n)
+        acc += n
+    return out
+
+
+def run_varlen_workload(args) -> None:
+    """65,536 packed tokens of causal attention on one GPU (QH=32, KVH=8, d=128), forward +
+    backward through ``forward_varlen`` / ``backward_varlen``; inputs resident in HBM."""
+    import min_fa3_op
+    from min_fa3_demo_b200 import _cabi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    _cabi.load()
+    qh, kvh = 32, 8
+    lens = varlen_lengths()
+    total = sum(lens)
+    cu_list = [0]
+    for n in lens:
+        cu_list.append(cu_list[-1] + n)
+    cu = torch.tensor(cu_list, dtype=torch.int32)
+    cud = cu.to(dev)
+    gen = torch.Generator(device=dev).manual_seed(3)
+    q = torch.randn(total, qh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    k = torch.randn(total, kvh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn(total, kvh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    dout = torch.randn(total, qh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    max_len = max(lens)
+
+    def step():
+        out, lse = min_fa3_op.forward_varlen(q, k, v, cud, cud, max_len, max_len, True, cu_seqlens_q_host=cu,
+                                             cu_seqlens_k_host=cu, return_lse=True)
+        return min_fa3_op.backward_varlen(dout, q, k, v, out, lse, cud, cud, max_len, max_len, True)
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark_begin()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.mark_end()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    vis = sum(n * (n + 1) / 2 for n in lens)
+    flops = 14.0 * qh * 128 * vis
+    burst, sustained, peak_kind = measured_peaks()
+    value = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"varlen_causal_T{total}_docs{len(lens)}_QH{qh}_KVH{kvh}_D128",
+                   "longest_document": max_len, "shortest_document": min(lens),
+                   "l2": "inputs larger than L2", "flops_per_step_per_gpu": flops},
+        "tflops_per_gpu": value,
+        "pct_of_bf16_peak": {f"{peak_kind}_burst": 100.0 * value / burst,
+                             f"{peak_kind}_sustained": 100.0 * value / sustained if sustained else None,
+                             "nominal_dense_2250": 100.0 * value / NOMINAL_BF16_TFLOPS},
+        "gpu_launches": 6 * args.steps,
+        "gpu_launches_note": "per step: 2 x varlen_plan_kernel, fwd_kernel, bwd_preprocess_kernel, bwd_kernel, "
+                             "bwd_postprocess_kernel",
+        "clocks": clocks}), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -503,20 +627,28 @@ def main() -> None:
                         help="time budget of the CPU baseline sample (N=1 only)")
     parser.add_argument("--batch", type=int, default=None,
                         help="override the per-GPU batch (smaller cases for profiler captures)")
-    parser.add_argument("--workload", choices=("bshd", "ring"), default="bshd",
-                        help="bshd: config 2 replicas (default); ring: one long causal sequence over N ranks")
+    parser.add_argument("--workload", choices=("bshd", "varlen", "ring", "ring_varlen"), default="bshd",
+                        help="bshd: config 2 replicas (default); varlen: config 3 (65,536 packed tokens, 1 GPU); "
+                             "ring: config 4, one long causal sequence over N ranks; ring_varlen: config 5, "
+                             "131,072 packed tokens placed on hierarchical sub-rings over N ranks")
+    parser.add_argument("--non-causal", action="store_true", help="bshd workload without the causal mask")
     parser.add_argument("--ring-tokens", type=int, default=131072)
     parser.add_argument("--ring-comm-sm", type=int, default=8)
     parser.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
     parser.add_argument("--skip-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
     args = parser.parse_args()
+    if args.non_causal:
+        WORKLOAD["causal"] = False
+        WORKLOAD["name"] = WORKLOAD["name"].replace("bshd_causal", "bshd_noncausal")
     if args.batch is not None:
         WORKLOAD["batch"] = args.batch
         WORKLOAD["name"] = WORKLOAD["name"].replace("_B4_", f"_B{args.batch}_")
     if args.impl == "reference":
         run_reference_arm(args)
-    elif args.workload == "ring":
+    elif args.workload in ("ring", "ring_varlen"):
         run_ring_workload(args)
+    elif args.workload == "varlen":
+        run_varlen_workload(args)
     else:
         run_cuda_arm(args)
 
