@@ -141,15 +141,19 @@ __device__ __forceinline__ BwdWork bwd_decode_work(const BwdParams& p, int w) {
     // fp32 dQ accumulator they share resident in L2.  BSHD applies this per batch element.
     const int entries = p.cu_seqlens_q == nullptr ? p.num_entries_host : *p.num_entries_dev;
     int per_batch = entries, b_idx = 0;
-    if (p.cu_seqlens_q == nullptr && p.ring_docs == nullptr) {
+    const bool bshd = p.cu_seqlens_q == nullptr && p.ring_docs == nullptr;
+    if (bshd) {
         per_batch = (p.seqlen_k + kTileN - 1) / kTileN;
         b_idx = w / (per_batch * p.heads_k);
         w -= b_idx * per_batch * p.heads_k;
     }
-    const int per_sg = per_batch * p.sg_heads;
+    // The last batch element is scheduled as one group over all heads: its most expensive items
+    // then start while plenty of work is left, which keeps the tail of the launch short.
+    const int sg_heads = (bshd && b_idx == p.batch - 1) ? p.heads_k : p.sg_heads;
+    const int per_sg = per_batch * sg_heads;
     const int sg = w / per_sg;
-    const int sg_base = sg * p.sg_heads;
-    const int sg_cnt = min(p.sg_heads, p.heads_k - sg_base);
+    const int sg_base = sg * sg_heads;
+    const int sg_cnt = min(sg_heads, p.heads_k - sg_base);
     const int sg_r = w - sg * per_sg;
     int entry = sg_r / sg_cnt;
     wk.head_k = sg_base + (sg_r - entry * sg_cnt);
