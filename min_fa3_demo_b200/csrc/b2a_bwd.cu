@@ -32,6 +32,7 @@ struct BwdLayout {
     size_t lse2_off;
     size_t dpsum_off;
     size_t dq_accum_off;
+    size_t dq_sem_off;     // int per (query head, 128-row query tile): deterministic dQ order
     size_t total;
     int padded_q;
     int entries_cap;
@@ -57,6 +58,8 @@ BwdLayout bwd_layout(int batch, int seqlen_q, int total_q, int total_k, int head
     off += align_up(vec_bytes, 256);
     l.dq_accum_off = off;
     off += vec_bytes * kHeadDim;
+    l.dq_sem_off = off;
+    off += align_up(static_cast<size_t>(heads_q) * (l.padded_q / kTileM) * sizeof(int), 256);
     l.total = align_up(off, 256);
     return l;
 }
@@ -150,6 +153,12 @@ int b2a_bwd(const b2a_bwd_args* a, void* cuda_stream) {
     B2A_CUDA_OK(cudaMemsetAsync(dq_accum, 0,
                                 static_cast<size_t>(a->heads_q) * lay.padded_q * kHeadDim * sizeof(float),
                                 stream));
+    int* dq_sem = nullptr;
+    if (a->deterministic) {
+        dq_sem = reinterpret_cast<int*>(ws + lay.dq_sem_off);
+        B2A_CUDA_OK(cudaMemsetAsync(dq_sem, 0, static_cast<size_t>(a->heads_q) * (lay.padded_q / kTileM) * sizeof(int),
+                                    stream));
+    }
 
     // Preprocess.
     BwdPreParams pre{};
@@ -181,6 +190,7 @@ int b2a_bwd(const b2a_bwd_args* a, void* cuda_stream) {
     p.dk = static_cast<__nv_bfloat16*>(a->dk);
     p.dv = static_cast<__nv_bfloat16*>(a->dv);
     p.dq_accum = dq_accum;
+    p.dq_sem = dq_sem;
     p.lse2 = lse2;
     p.dpsum = dpsum;
     p.cu_seqlens_q = a->cu_seqlens_q;

@@ -50,6 +50,8 @@ struct BwdParams {
     __nv_bfloat16* dk;             // [tokens_k, heads_k, 128]
     __nv_bfloat16* dv;
     float* dq_accum;               // see layout above
+    int* dq_sem;                   // deterministic mode: per (query head, query tile) count of key blocks
+                                   // already added, zeroed before launch; null otherwise
     const float* lse2;             // [heads_q, padded_q]  (LSE * log2 e; +inf = row contributes nothing)
     const float* dpsum;            // [heads_q, padded_q]  rowsum(dO * O)
     const int* cu_seqlens_q;
@@ -272,6 +274,26 @@ struct __align__(1024) BwdShared {
     uint32_t abort_flag;
 };
 static_assert(sizeof(BwdShared) <= 232448, "backward shared storage exceeds the 227 KiB opt-in limit");
+
+// Bounded wait until a global counter reaches `value` (acquire at GPU scope).
+__device__ __forceinline__ bool value_wait(const WaitCtx& ctx, const int* counter, int value, uint32_t tag) {
+    const uint32_t start = global_timer_lo();
+    uint32_t polls = 0;
+    while (true) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= value) return true;
+        if ((++polls & 0xFu) == 0u) {
+            if (ld_shared_volatile_u32(ctx.abort_smem) != 0u) return false;
+            if (global_timer_lo() - start > ctx.timeout_ns) {
+                st_shared_volatile_u32(ctx.abort_smem, 1u);
+                set_status(ctx.status, kStatusTimeout, (tag << 12) | (blockIdx.x & 0xFFFu));
+                return false;
+            }
+        }
+        __nanosleep(64);
+    }
+}
 
 // Copy role of a ring-mode backward CTA (same protocol as the forward's): six 32 KiB slots laid
 // over the K ... dO tile buffers and the dQ staging area, one loading thread, one storing thread, per-block ready flags.
@@ -660,6 +682,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t dq_tmem = tmem_base + lane_base + kColDP;
         uint32_t dq_cnt = 0;
+        int* prev_sem = nullptr;   // deterministic mode, thread 256: tile whose counter is still to be published
+        int prev_val = 0;
         bool ok = true;
         PH_DECL(4)   // 0 other, 1 wait dq_full, 2 load + arrive, 3 reductions
         for (uint32_t it = 0; ok; ++it) {
@@ -696,6 +720,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&sh.dq_drained));
                 PH_MARK(2);
+                // Deterministic mode: the key blocks of a document add into a dQ tile in ascending
+                // order.  Block n waits until the tile's counter says n blocks have been added.
+                // Work items are handed out in ascending block order per (document, head), so the
+                // blocks waited for are always running already; the wait is bounded all the same.
+                int* sem = nullptr;
+                const int blk_index = wk.n0 / kTileN;
+                if (p.dq_sem != nullptr) {
+                    sem = p.dq_sem + static_cast<long long>(hq) * pad_tiles + (wk.q_pad_begin + q_local) / kTileM;
+                    // A wait that runs out raises the CTA's abort flag and status word; the warpgroup
+                    // still goes through this step's barriers together and stops at its next wait.
+                    if (threadIdx.x == 256) (void)value_wait(wctx, sem, blk_index, 26);
+                }
                 // Four chunks of 32 columns go through two 16 KiB staging buffers whose layout
                 // equals the accumulator's ([8 column quads][128 rows][4 floats]); one thread hands
                 // each to the bulk-copy engine as an fp32 reduce-add into global memory, so the
@@ -720,7 +756,26 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                         bulk_commit_group();
                     }
                 }
+                if (sem != nullptr && threadIdx.x == 256) {
+                    // Publish the previous tile once its four reductions are performed (the four of
+                    // this tile may still be in flight), so the warpgroup never waits for its own
+                    // latest additions.
+                    if (prev_sem != nullptr) {
+                        bulk_wait_group<4>();
+                        fence_proxy_async_all();
+                        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(prev_sem), "r"(prev_val) : "memory");
+                    }
+                    prev_sem = sem;
+                    prev_val = blk_index + 1;
+                }
                 PH_MARK(3);
+            }
+            if (prev_sem != nullptr) {
+                // End of the work item: publish its last tile (thread 256 only holds prev_sem).
+                bulk_wait_group<0>();
+                fence_proxy_async_all();
+                asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(prev_sem), "r"(prev_val) : "memory");
+                prev_sem = nullptr;
             }
         }
         if (threadIdx.x == 256) bulk_wait_group<0>();   // all reductions performed before the CTA ends

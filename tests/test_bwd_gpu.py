@@ -170,3 +170,45 @@ def test_full_size_backward_properties(causal):
         rq, rk, rv = orc.bshd_backward(qs[:, :, :4].cpu(), ks[:, :, :1].cpu(), vs[:, :, :1].cpu(),
                                        ds[:, :, :4].cpu(), True)
         assert (g2[0][:, :, :4].float().cpu() - rq).abs().max().item() <= 3e-2
+
+
+# --------------------------------------------------------------------------------------
+# deterministic=True: dQ is accumulated in ascending key-block order, so repeated calls are
+# bitwise identical (the reference checks four repeats:
+# scripts/test_min_fa3_backward.py:77-93); the result must still meet the accuracy rule.
+# --------------------------------------------------------------------------------------
+@pytest.mark.parametrize("causal", [False, True])
+def test_bshd_backward_deterministic_repeats_bitwise(causal):
+    b, s, qh, kvh = 2, 2048, 8, 2
+    q, k, v, dout = make_bshd(99, b, s, qh, kvh)
+    qc, kc, vc, dc = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
+    out, lse = min_fa3_op.forward(qc, kc, vc, causal, return_lse=True)
+    runs = [min_fa3_op.backward(dc, qc, kc, vc, out, lse, causal, deterministic=True) for _ in range(4)]
+    torch.cuda.synchronize()
+    for other in runs[1:]:
+        for name, a, b_ in zip(("dq", "dk", "dv"), runs[0], other):
+            assert torch.equal(a, b_), f"{name} differs between repeated deterministic calls"
+    rq, rk, rv = orc.bshd_backward(q, k, v, dout, causal)
+    e = orc.bf16_attention_error(q, k, v, causal, dout)
+    assert_within("dQ", runs[0][0], rq, e["dq"])
+    assert_within("dK", runs[0][1], rk, e["dk"])
+    assert_within("dV", runs[0][2], rv, e["dv"])
+
+
+def test_varlen_backward_deterministic_repeats_bitwise():
+    lengths = [1500, 77, 640, 1, 2049, 333]
+    q, k, v, dout, cu = make_varlen(17, lengths, 8, 2)
+    qc, kc, vc, dc, cuc = q.cuda(), k.cuda(), v.cuda(), dout.cuda(), cu.cuda()
+    out, lse = min_fa3_op.forward_varlen(qc, kc, vc, cuc, cuc, max(lengths), max(lengths), True,
+                                         cu_seqlens_q_host=cu, cu_seqlens_k_host=cu, return_lse=True)
+    runs = [min_fa3_op.backward_varlen(dc, qc, kc, vc, out, lse, cuc, cuc, max(lengths), max(lengths), True,
+                                       deterministic=True) for _ in range(4)]
+    plain = min_fa3_op.backward_varlen(dc, qc, kc, vc, out, lse, cuc, cuc, max(lengths), max(lengths), True)
+    torch.cuda.synchronize()
+    for other in runs[1:]:
+        for name, a, b_ in zip(("dq", "dk", "dv"), runs[0], other):
+            assert torch.equal(a, b_), f"{name} differs between repeated deterministic calls"
+    # Same arithmetic as the default path up to the order of the fp32 dQ additions.
+    assert torch.equal(runs[0][1], plain[1]) and torch.equal(runs[0][2], plain[2])
+    scale = max(1.0, plain[0].float().abs().max().item())
+    assert (runs[0][0].float() - plain[0].float()).abs().max().item() <= 2.0 ** -6 * scale
