@@ -282,7 +282,7 @@ def run_cuda_arm(args) -> None:
     from min_fa3_demo_b200.host_pipeline import HostPipeline
     host_out = {"out": torch.empty_like(host["q"]).pin_memory(), "dq": torch.empty_like(host["q"]).pin_memory(),
                 "dk": torch.empty_like(host["k"]).pin_memory(), "dv": torch.empty_like(host["v"]).pin_memory()}
-    pipeline = HostPipeline(dev, s, qh, kvh)
+    pipeline = HostPipeline(dev, s, qh, kvh, head_groups=args.e2e_head_groups)
 
     def step_e2e():
         # Host q, k, v, dout in; host out, dq, dk, dv back: upload, kernels and download of
@@ -340,7 +340,7 @@ def run_cuda_arm(args) -> None:
         "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12 if e2e_ms else None, "unit": UNIT,
                 "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "api": "min_fa3_demo_b200.host_pipeline.HostPipeline.run (pinned host tensors in and out; "
-                       "batch elements pipelined over upload / compute / download streams)"},
+                       "(batch element, KV-head group) chunks pipelined over upload / compute / download streams)"},
         "gpu_launches": 4 * args.steps,
         "gpu_launches_note": "per step: fwd_kernel, bwd_preprocess_kernel, bwd_kernel, bwd_postprocess_kernel",
         "clocks": clocks,
@@ -635,6 +635,8 @@ def main() -> None:
     parser.add_argument("--ring-tokens", type=int, default=131072)
     parser.add_argument("--ring-comm-sm", type=int, default=8)
     parser.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
+    parser.add_argument("--e2e-head-groups", type=int, default=2,
+                        help="chunks per batch element in the host-buffer pipeline (must divide the KV heads)")
     parser.add_argument("--skip-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
     args = parser.parse_args()
     if args.non_causal:

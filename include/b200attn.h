@@ -171,6 +171,17 @@ int b2a_ipc_import(const unsigned char* handle64, uint64_t offset, void** out_pt
 int b2a_ipc_close(void* ptr, uint64_t offset);
 
 /*
+ * Asynchronous strided copy between pinned host memory and device memory (or device to device):
+ * `rows` rows of `row_bytes` bytes, the rows `src_pitch` / `dst_pitch` bytes apart.  A thin
+ * wrapper over the runtime's 2-D memcpy for callers that move a subset of heads of a
+ * [tokens, heads, 128] host tensor without staging it (the host-buffer pipeline of this
+ * package).  No counterpart in the reference, whose operators take device tensors only.
+ * kind: 1 host->device, 2 device->host, 3 device->device.
+ */
+int b2a_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
+                size_t rows, int32_t kind, void* cuda_stream);
+
+/*
  * Copy `bytes` (multiple of 16) from `src` (typically a peer pointer) to local `dst` with
  * `num_blocks` CTAs of bulk asynchronous copies through shared memory.  Replaces
  * RemoteLoadTileKernel / RemoteLoadVecKernel (csrc/parallel/remote_load.cu:21-128).

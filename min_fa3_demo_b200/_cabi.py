@@ -166,6 +166,7 @@ SIGNATURES = {
     "b2a_ipc_import": (c_int32, [c_void_p, ctypes.c_uint64, POINTER(c_void_p)]),
     "b2a_ipc_close": (c_int32, [c_void_p, ctypes.c_uint64]),
     "b2a_peer_copy": (c_int32, [c_void_p, c_void_p, c_size_t, c_int32, c_void_p, c_void_p]),
+    "b2a_copy_2d": (c_int32, [c_void_p, c_size_t, c_void_p, c_size_t, c_size_t, c_size_t, c_int32, c_void_p]),
     "b2a_ring_fwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32]),
     "b2a_ring_fwd": (c_int32, [POINTER(RingFwdArgs), c_void_p]),
     "b2a_ring_bwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),

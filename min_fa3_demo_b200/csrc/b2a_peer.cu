@@ -120,6 +120,20 @@ int b2a_ipc_close(void* ptr, uint64_t offset) {
     return B2A_OK;
 }
 
+int b2a_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
+                size_t rows, int32_t kind, void* cuda_stream) {
+    using namespace b2a;
+    B2A_REQUIRE(dst != nullptr && src != nullptr, "dst and src must not be NULL");
+    B2A_REQUIRE(row_bytes > 0 && rows > 0, "row_bytes and rows must be positive");
+    B2A_REQUIRE(dst_pitch >= row_bytes && src_pitch >= row_bytes, "pitches must be at least row_bytes");
+    B2A_REQUIRE(kind >= 1 && kind <= 3, "kind must be 1 (host->device), 2 (device->host) or 3 (device->device)");
+    const cudaMemcpyKind k = kind == 1 ? cudaMemcpyHostToDevice
+                             : kind == 2 ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    B2A_CUDA_OK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows, k,
+                                  static_cast<cudaStream_t>(cuda_stream)));
+    return B2A_OK;
+}
+
 int b2a_peer_copy(void* dst, const void* src, size_t bytes, int32_t num_blocks, unsigned int* status,
                   void* cuda_stream) {
     using namespace b2a;

@@ -13,15 +13,16 @@ from min_fa3_demo_b200.host_pipeline import HostPipeline
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("groups", [1, 2])
 @pytest.mark.parametrize("causal", [True, False])
-def test_pipeline_equals_direct_calls(causal):
+def test_pipeline_equals_direct_calls(causal, groups):
     b, s, qh, kvh = 5, 384, 8, 2
     q, k, v, dout = make_bshd(77, b, s, qh, kvh)
     host_in = {"q": q.pin_memory(), "k": k.pin_memory(), "v": v.pin_memory(), "dout": dout.pin_memory()}
     host_out = {"out": torch.empty_like(q).pin_memory(), "dq": torch.empty_like(q).pin_memory(),
                 "dk": torch.empty_like(k).pin_memory(), "dv": torch.empty_like(v).pin_memory()}
     dev = torch.device("cuda", 0)
-    pipe = HostPipeline(dev, s, qh, kvh)
+    pipe = HostPipeline(dev, s, qh, kvh, head_groups=groups)
     out, lse = min_fa3_op.forward(q.cuda(), k.cuda(), v.cuda(), causal, return_lse=True)
     dq, dk, dv = min_fa3_op.backward(dout.cuda(), q.cuda(), k.cuda(), v.cuda(), out, lse, causal)
     for _ in range(2):                      # second pass reuses slots, streams and events
