@@ -143,6 +143,17 @@ __device__ __forceinline__ BwdWork bwd_decode_work(const BwdParams& p, int w) {
     const int entries = p.cu_seqlens_q == nullptr ? p.num_entries_host : *p.num_entries_dev;
     int per_batch = entries, b_idx = 0;
     const bool bshd = p.cu_seqlens_q == nullptr && p.ring_docs == nullptr;
+    if (bshd && p.dq_sem != nullptr) {
+        // Deterministic mode: key block major, then batch element, then head.  A block waits for
+        // the previous block of the same (batch element, head); spreading the running CTAs over
+        // the batch keeps those chains short.
+        const int nnb = (p.seqlen_k + kTileN - 1) / kTileN;
+        const int per_n = p.batch * p.heads_k;
+        const int ni = w / per_n;
+        const int r = w - ni * per_n;
+        const int b = r / p.heads_k;
+        w = (b * nnb + ni) * p.heads_k + (r - b * p.heads_k);   // index in the default order
+    }
     if (bshd) {
         per_batch = (p.seqlen_k + kTileN - 1) / kTileN;
         b_idx = w / (per_batch * p.heads_k);
