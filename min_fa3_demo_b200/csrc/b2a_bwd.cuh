@@ -68,6 +68,7 @@ struct BwdParams {
     int causal;
     int num_entries_host;
     int sg_heads;      // key/value heads per scheduling supergroup (1..heads_k)
+    int batch_minor;   // BSHD: hand out work key block major, batch element minor (deterministic mode)
     int padded_q;                  // padded query rows per head (multiple of 128)
     float scale;
     float scale_log2;
@@ -143,7 +144,7 @@ __device__ __forceinline__ BwdWork bwd_decode_work(const BwdParams& p, int w) {
     const int entries = p.cu_seqlens_q == nullptr ? p.num_entries_host : *p.num_entries_dev;
     int per_batch = entries, b_idx = 0;
     const bool bshd = p.cu_seqlens_q == nullptr && p.ring_docs == nullptr;
-    if (bshd && p.dq_sem != nullptr) {
+    if (bshd && p.batch_minor != 0) {
         // Deterministic mode: key block major, then batch element, then head.  A block waits for
         // the previous block of the same (batch element, head); spreading the running CTAs over
         // the batch keeps those chains short.
