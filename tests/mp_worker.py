@@ -311,7 +311,44 @@ def case_mega_ring_bwd(rank, world, dev):
         barrier(world)
 
 
-CASES = {"mega_ring_bwd": case_mega_ring_bwd, "mega_ring_fwd": case_mega_ring_fwd, "remote_load": case_remote_load, "ring_steps": case_ring_steps}
+def case_ring_autograd(rank, world, dev):
+    """The differentiable context-parallel front end (RingAttention): gradients of this rank's
+    shard against fp32 autograd over the global documents; two forward/backward rounds through the
+    same object exercise the arena reuse and the accumulator reset it performs."""
+    from min_fa3_demo_b200.autograd import RingAttention
+    qh, kvh = 8, 2
+    causal = True
+    docs = ring_docs_for(world)
+    q, k, v, dout, cu, odocs = build_problem(world, rank, docs, qh, kvh, causal, BASE_SEED + 21)
+    lens = (cu[1:] - cu[:-1]).tolist()
+    ring = RingAttention(2048, kvh, is_causal=causal, device=dev)
+    ok = True
+    for rep in range(2):
+        qd, kd, vd = (t.to(dev).requires_grad_() for t in (q, k, v))
+        out = ring(qd, kd, vd, lens, [d[0] for d in docs], [d[1] for d in docs], [d[2] for d in docs])
+        out.backward(dout.to(dev))
+        torch.cuda.synchronize()
+        rq, rkk, rvv, ro = [], [], [], []
+        for (qg, kg, vg, dg, pos) in odocs:
+            qf, kf, vf = (t.float().requires_grad_() for t in (qg, kg, vg))
+            p_all = torch.arange(qg.size(0))
+            o, _ = orc.attention_positions(qf, kf, vf, p_all, p_all)
+            gq, gk, gv = torch.autograd.grad(o, (qf, kf, vf), dg.float())
+            rq.append(gq[pos]); rkk.append(gk[pos]); rvv.append(gv[pos]); ro.append(o.detach()[pos])
+        if rq:
+            for name, got, ref in (("out", out.detach(), torch.cat(ro)), ("dq", qd.grad, torch.cat(rq)),
+                                   ("dk", kd.grad, torch.cat(rkk)), ("dv", vd.grad, torch.cat(rvv))):
+                err = (got.float().cpu() - ref).abs().max().item()
+                tol = 4e-2 * max(1.0, ref.abs().max().item())
+                if not err <= tol:
+                    print(f"[rank {rank}] ring_autograd rep={rep} {name}: err {err:.3e} tol {tol:.3e}", flush=True)
+                    ok = False
+        barrier(world)
+    vote(ok, world, f"ring_autograd world={world}", rank)
+    barrier(world)
+
+
+CASES = {"ring_autograd": case_ring_autograd, "mega_ring_bwd": case_mega_ring_bwd, "mega_ring_fwd": case_mega_ring_fwd, "remote_load": case_remote_load, "ring_steps": case_ring_steps}
 
 
 def main(argv):

@@ -31,7 +31,7 @@ def run_worker(world: int, cases: list[str]) -> None:
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
 
 
-@pytest.mark.parametrize("case", ["mega_ring_fwd", "remote_load", "ring_steps", "mega_ring_bwd"])
+@pytest.mark.parametrize("case", ["mega_ring_fwd", "remote_load", "ring_steps", "mega_ring_bwd", "ring_autograd"])
 def test_single_rank(case):
     run_worker(1, [case])
 
@@ -45,6 +45,6 @@ def _multi_world() -> int:
 
 
 @pytest.mark.skipif(_multi_world() == 0, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("case", ["remote_load", "ring_steps", "mega_ring_fwd", "mega_ring_bwd"])
+@pytest.mark.parametrize("case", ["remote_load", "ring_steps", "mega_ring_fwd", "mega_ring_bwd", "ring_autograd"])
 def test_multi_rank(case):
     run_worker(_multi_world(), [case])
