@@ -348,7 +348,74 @@ def case_ring_autograd(rank, world, dev):
     barrier(world)
 
 
-CASES = {"ring_autograd": case_ring_autograd, "mega_ring_bwd": case_mega_ring_bwd, "mega_ring_fwd": case_mega_ring_fwd, "remote_load": case_remote_load, "ring_steps": case_ring_steps}
+def case_empty_rank(rank, world, dev):
+    """A rank that holds no token of any document still takes part in the forward and in the
+    backward's completion protocol (reference: csrc/mega_ring_min_fa3_varlen_ring_bindings.cu:568-575)."""
+    from min_fa3_demo_b200.min_fa3_op import check_device_status
+    if world < 2:
+        if rank == 0:
+            print("empty_rank: needs at least 2 ranks, skipped", flush=True)
+        return
+    qh, kvh, causal = 4, 2, True
+    members = world - 1 if world - 1 in (1, 2, 4) else (4 if world == 8 else 1)
+    docs = []
+    if members > 1:
+        docs.append((members * 512, members, 0))
+    docs += [(384, 1, 0), (256, 1, max(members - 1, 0))]          # the last rank gets nothing
+    q, k, v, dout, cu, odocs = build_problem(world, rank, docs, qh, kvh, causal, BASE_SEED + 31)
+    assert (rank == world - 1) == (q.size(0) == 0), "test layout: exactly the last rank is empty"
+    cap = 2048
+    sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    rk, rv = make_arena(world, rank, cap, k, v, dev)
+    acc_k = min_fa3_op.TKParallelTensor([kvh * cap * 128], torch.float32, dev.index, world, False)
+    acc_v = min_fa3_op.TKParallelTensor([kvh * cap * 128], torch.float32, dev.index, world, False)
+    done = min_fa3_op.TKParallelTensor([1], torch.int32, dev.index, world, False)
+    g, s_, st = meta(docs)
+    lens = (cu[1:] - cu[:-1]).tolist()
+    mx = max(max(lens), 1)
+    qd, dd, cud = q.to(dev), dout.to(dev), cu.to(dev)
+    barrier(world)
+    out, lse = min_fa3_op.forward_varlen_mega_ring(
+        qd, rk.data_, rv.data_, cud, cud, mx, mx, causal, cu_seqlens_q_host=cu, cu_seqlens_k_host=cu,
+        remote_k=rk, remote_v=rv, num_comp_sm=sm - 8, num_comm_sm=8, global_seqlens_host=g,
+        ring_sizes_host=s_, ring_starts_host=st, return_lse=True)
+    acc_k.data_.zero_(); acc_v.data_.zero_(); done.data_.zero_()
+    barrier(world)
+    dq, dk, dv = min_fa3_op.backward_varlen_mega_ring(
+        dd, qd, rk.data_, rv.data_, out, lse, cud, cud, mx, mx, cu_seqlens_q_host=cu, cu_seqlens_k_host=cu,
+        remote_k=rk, remote_v=rv, remote_dk_accum=acc_k, remote_dv_accum=acc_v, remote_dkv_completion=done,
+        num_comp_sm=sm - 8, num_comm_sm=8, global_seqlens_host=g, ring_sizes_host=s_, ring_starts_host=st,
+        is_causal=causal)
+    torch.cuda.synchronize()
+    ok = done.data_.item() == world and tuple(out.shape) == tuple(q.shape) and tuple(dk.shape) == tuple(k.shape)
+    try:
+        check_device_status(min_fa3_op.backward_varlen_mega_ring.last_workspace)
+    except RuntimeError as exc:
+        print(f"[rank {rank}] device status: {exc}", flush=True)
+        ok = False
+    if odocs:
+        ref_out, _ = oracle_forward(odocs, causal)
+        err = (out.float().cpu() - ref_out).abs().max().item()
+        if not err <= 3e-2:
+            print(f"[rank {rank}] empty_rank out err {err:.3e}", flush=True)
+            ok = False
+        rq = []
+        for (qg, kg, vg, dg, pos) in odocs:
+            qf, kf, vf = (t.float().requires_grad_() for t in (qg, kg, vg))
+            p_all = torch.arange(qg.size(0))
+            o, _ = orc.attention_positions(qf, kf, vf, p_all, p_all)
+            rq.append(torch.autograd.grad(o, qf, dg.float())[0][pos])
+        ref = torch.cat(rq)
+        err = (dq.float().cpu() - ref).abs().max().item()
+        if not err <= 4e-2 * max(1.0, ref.abs().max().item()):
+            print(f"[rank {rank}] empty_rank dq err {err:.3e}", flush=True)
+            ok = False
+    barrier(world)
+    vote(ok, world, f"empty_rank world={world}", rank)
+    barrier(world)
+
+
+CASES = {"empty_rank": case_empty_rank, "ring_autograd": case_ring_autograd, "mega_ring_bwd": case_mega_ring_bwd, "mega_ring_fwd": case_mega_ring_fwd, "remote_load": case_remote_load, "ring_steps": case_ring_steps}
 
 
 def main(argv):

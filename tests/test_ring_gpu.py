@@ -45,6 +45,6 @@ def _multi_world() -> int:
 
 
 @pytest.mark.skipif(_multi_world() == 0, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("case", ["remote_load", "ring_steps", "mega_ring_fwd", "mega_ring_bwd", "ring_autograd"])
+@pytest.mark.parametrize("case", ["remote_load", "ring_steps", "mega_ring_fwd", "mega_ring_bwd", "ring_autograd", "empty_rank"])
 def test_multi_rank(case):
     run_worker(_multi_world(), [case])
