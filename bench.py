@@ -466,6 +466,63 @@ def run_ring_workload(args) -> None:
             done.data_.zero_()
             barrier()
 
+    if args.ring_impl == "allgather" and world > 1:
+        if varlen:
+            raise SystemExit("--ring-impl allgather is implemented for the single-sequence ring workload")
+        # Comparison baseline built from library collectives: every rank gathers all K/V (NCCL
+        # all_gather), restores global token order, and runs plain varlen attention for its two
+        # zigzag halves as two documents whose keys are the global prefix each half may see
+        # (causal, bottom-right aligned); backward scatters dK/dV of the two prefixes back to
+        # global order and reduce_scatters them to their owners.
+        half = local // 2
+        chunks = 2 * world
+        kv_shape = (world, local, kvh, 128)
+        # chunk c of the global sequence lives on rank (c if c < world else chunks-1-c), front or back half
+        order = torch.empty(chunks, dtype=torch.long)
+        for c in range(chunks):
+            r_own = c if c < world else chunks - 1 - c
+            order[c] = r_own * 2 + (0 if c < world else 1)
+        order_dev = order.to(dev)
+        inv_dev = torch.argsort(order_dev)
+        n_front, n_back = (rank + 1) * half, (chunks - rank) * half
+        cu_q2 = torch.tensor([0, half, 2 * half], dtype=torch.int32)
+        cu_k2 = torch.tensor([0, n_front, n_front + n_back], dtype=torch.int32)
+        cu_q2d, cu_k2d = cu_q2.to(dev), cu_k2.to(dev)
+        gk = torch.empty(kv_shape, dtype=torch.bfloat16, device=dev)
+        gv = torch.empty(kv_shape, dtype=torch.bfloat16, device=dev)
+        state = {}
+
+        def global_order(t):      # [world, local, ...] in rank order -> [chunks * half, ...] in token order
+            return t.view(chunks, half, kvh, 128).index_select(0, order_dev).reshape(chunks * half, kvh, 128)
+
+        def fwd():
+            dist.all_gather_into_tensor(gk, k)
+            dist.all_gather_into_tensor(gv, v)
+            kg, vg = global_order(gk), global_order(gv)
+            k2 = torch.cat([kg[:n_front], kg[:n_back]])
+            v2 = torch.cat([vg[:n_front], vg[:n_back]])
+            state["k2"], state["v2"] = k2, v2
+            return min_fa3_op.forward_varlen(q, k2, v2, cu_q2d, cu_k2d, half, n_back, True, cu_seqlens_q_host=cu_q2,
+                                             cu_seqlens_k_host=cu_k2, return_lse=True)
+
+        def bwd(out, lse):
+            dq, dk2, dv2 = min_fa3_op.backward_varlen(dout, q, state["k2"], state["v2"], out, lse, cu_q2d, cu_k2d,
+                                                      half, n_back, True)
+            outs = []
+            for d2 in (dk2, dv2):
+                g = torch.zeros(chunks * half, kvh, 128, dtype=torch.float32, device=dev)
+                g[:n_front] += d2[:n_front].float()
+                g[:n_back] += d2[n_front:].float()
+                # back to rank order [world, local, ...] and reduce_scatter to the owners
+                g = g.view(chunks, half, kvh, 128).index_select(0, inv_dev).reshape(world, local, kvh, 128)
+                mine = torch.empty(local, kvh, 128, dtype=torch.float32, device=dev)
+                dist.reduce_scatter_tensor(mine, g)
+                outs.append(mine.to(torch.bfloat16))
+            return dq, outs[0], outs[1]
+
+        def reset():
+            pass
+
     barrier()
     e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     fwd_ms, bwd_ms = [], []
@@ -514,7 +571,9 @@ def run_ring_workload(args) -> None:
                                        "K/V pulled over NVLink in-kernel" if varlen else
                                        f"cp{world} zigzag ring, K/V pulled over NVLink in-kernel")
                        if world > 1 else "single GPU (efficiency baseline)",
-                       "copy_ctas": args.ring_comm_sm if world > 1 else 0,
+                       "copy_ctas": args.ring_comm_sm if world > 1 and args.ring_impl == "fused" else 0,
+                       "exchange": ("in-kernel peer loads (fused)" if args.ring_impl == "fused" else
+                                    "NCCL all_gather of K/V + reduce_scatter of dK/dV (comparison baseline)"),
                        "l2": "inputs larger than L2"},
             "tflops_per_gpu": value / world, "fwd_ms": fm, "bwd_ms": bm,
             "fwd_tflops_per_gpu": f_flops / (fm * 1e-3) / 1e12 / world,
@@ -634,6 +693,10 @@ def main() -> None:
     parser.add_argument("--non-causal", action="store_true", help="bshd workload without the causal mask")
     parser.add_argument("--ring-tokens", type=int, default=131072)
     parser.add_argument("--ring-comm-sm", type=int, default=8)
+    parser.add_argument("--ring-impl", choices=("fused", "allgather"), default="fused",
+                        help="ring workload: fused = K/V pulled inside the attention launch (the product); "
+                             "allgather = comparison baseline, NCCL all_gather of K/V + plain varlen attention + "
+                             "NCCL reduce_scatter of dK/dV")
     parser.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
     parser.add_argument("--e2e-head-groups", type=int, default=2,
                         help="chunks per batch element in the host-buffer pipeline (must divide the KV heads)")

@@ -13,18 +13,22 @@ namespace {
 
 constexpr size_t kBwdSmemBytes = sizeof(BwdShared);
 
-// Key/value heads scheduled together ("supergroup").  Default: all of them, i.e. plain
-// most-expensive-first order over (key block, head).  Smaller groups were tried to keep the dQ
-// accumulator tiles that concurrently running CTAs add into within L2; measured on B200 at
-// B=2, S=8192, QH=32, KVH=8 they made things worse (DRAM traffic per launch 1.9 GB with 8 heads,
-// 5.3 GB with 3, 3.8 GB with 1; duration 2.33 / 2.52 / 2.42 ms), so the knob stays for
-// experiments only (environment variable B2A_BWD_SG_HEADS).
-int pick_sg_heads(int /*heads_q*/, int heads_k, long long /*q_rows*/) {
+// Key/value heads scheduled together ("supergroup"): as many as keep the fp32 dQ accumulator
+// rows that the concurrently running CTAs add into (query heads of the group x query rows x
+// 512 bytes) within about the size of L2.  Measured on B200 (QH=32, KVH=8): at S=8192 all 8 heads
+// together are best (B=2: 1.9 GB of DRAM traffic per launch against 5.3 GB with 3 heads and 3.8 GB
+// with 1; 2.33 / 2.52 / 2.42 ms); on one 131,072-token sequence 1 or 2 heads are best (329 / 331 ms
+// against 350 ms with all 8).  The environment variable B2A_BWD_SG_HEADS overrides the choice.
+int pick_sg_heads(int heads_q, int heads_k, long long q_rows) {
     if (const char* env = getenv("B2A_BWD_SG_HEADS")) {
         const int v = atoi(env);
         if (v >= 1) return v < heads_k ? v : heads_k;
     }
-    return heads_k;
+    const long long per_head = static_cast<long long>(heads_q / heads_k) * (q_rows > 0 ? q_rows : 1) * 512;
+    const long long budget = 160ll << 20;
+    long long n = budget / per_head;
+    if (n < 1) n = 1;
+    return n < heads_k ? static_cast<int>(n) : heads_k;
 }
 
 struct BwdLayout {

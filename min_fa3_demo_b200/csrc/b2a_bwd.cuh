@@ -138,9 +138,10 @@ __host__ __device__ __forceinline__ int bwd_padded_begin(int cu_begin, int doc) 
 
 __device__ __forceinline__ BwdWork bwd_decode_work(const BwdParams& p, int w) {
     BwdWork wk;
-    // Work order: key/value heads are taken `sg_heads` at a time ("supergroup", by default all
-    // heads at once); inside a supergroup the entries run in list order (most expensive first)
-    // with the head minor.  BSHD applies this per batch element.
+    // Work order: key/value heads are taken `sg_heads` at a time ("supergroup", sized by the host
+    // so that the dQ accumulator rows being added to stay within L2); inside a supergroup the
+    // entries run in list order (most expensive first) with the head minor.  BSHD applies this
+    // per batch element.
     const int entries = p.cu_seqlens_q == nullptr ? p.num_entries_host : *p.num_entries_dev;
     int per_batch = entries, b_idx = 0;
     const bool bshd = p.cu_seqlens_q == nullptr && p.ring_docs == nullptr;
