@@ -4,7 +4,7 @@
     python bench.py --impl reference --steps K --warmup W    # the reference's CPU attention
 
 One step is one forward + backward pass over the workload.  At every N the workload is
-BASELINE config 2 per GPU (BSHD, causal, B=4, S=8192, QH=32, KVH=8, d=128, bf16 N(0,1)
+benchmark configuration 2 per GPU (BSHD, causal, B=4, S=8192, QH=32, KVH=8, d=128, bf16 N(0,1)
 from a fixed seed): each rank owns an independent batch, there is no data-path collective,
 scaling is weak.  Printed numbers use the causal-discounted algorithmic FLOPs
 ``14 * QH * D * sum_docs L(L+1)/2`` per step (forward 4x, backward 10x).
@@ -356,7 +356,7 @@ def run_cuda_arm(args) -> None:
 
 
 # --------------------------------------------------------------------------------------
-# Ring context-parallel workload (BASELINE config 4)
+# Ring context-parallel workload (benchmark configuration 4)
 # --------------------------------------------------------------------------------------
 def run_ring_workload(args) -> None:
     """One 131,072-token causal sequence (QH=32, KVH=8, d=128), zigzag-sharded over the N ranks;
@@ -591,7 +591,7 @@ def run_ring_workload(args) -> None:
 
 
 # --------------------------------------------------------------------------------------
-# Packed varlen workload (BASELINE config 3)
+# Packed varlen workload (benchmark configuration 3)
 # --------------------------------------------------------------------------------------
 def varlen_lengths(total: int = 65536, seed: int = 0):
     """Document lengths of config 3: log-normal (median 1,500, sigma 1.2) clipped to

@@ -26,7 +26,7 @@ def fwd_bwd_bshd(q, k, v, dout, causal, **kw):
 @pytest.mark.parametrize("b,s,qh,kvh", [
     (1, 128, 32, 32),      # reference backward test default
     (1, 129, 4, 2),
-    (2, 1024, 16, 4),      # BASELINE config 1
+    (2, 1024, 16, 4),      # benchmark configuration 1
     (1, 333, 2, 1),
     (2, 640, 8, 8),
     (1, 1, 2, 2),

@@ -24,7 +24,7 @@ def run_bshd(q, k, v, causal, **kw):
 @pytest.mark.parametrize("b,s,qh,kvh", [
     (1, 128, 32, 32),      # reference test default shape
     (1, 129, 4, 2),        # one row past a tile
-    (2, 1024, 16, 4),      # BASELINE config 1
+    (2, 1024, 16, 4),      # benchmark configuration 1
     (1, 333, 2, 1),        # ragged, MQA
     (3, 640, 8, 8),
     (1, 1, 2, 2),          # single token
@@ -139,7 +139,7 @@ def test_forward_error_behaviour_on_gpu():
 
 
 # ---------------------------------------------------------------------------------------
-# BASELINE sizes: size-independent properties
+# Full benchmark sizes: size-independent properties
 # ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("causal", [False, True])
 def test_full_size_rows_against_oracle_and_properties(causal):
