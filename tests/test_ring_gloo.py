@@ -104,7 +104,7 @@ def _worker(rank: int, world: int, port: int, causal: bool, results) -> None:
 def test_two_rank_placement_sharding_and_exchange(causal):
     world = 2
     port = _free_port()
-    manager = mp.Manager()
+    manager = mp.get_context("spawn").Manager()
     results = manager.dict()
     mp.spawn(_worker, args=(world, port, causal, results), nprocs=world, join=True)
     assert set(results.keys()) == {0, 1}
