@@ -1,0 +1,47 @@
+"""The synthetic workloads of bench.py: shapes, length distributions and the algorithmic FLOP
+counts the reported TFLOPS are based on (14 * QH * D * sum over documents of L(L+1)/2 for causal
+attention, forward 4x and backward 10x of QH * D * visible pairs)."""
+from __future__ import annotations
+
+import importlib.util
+from pathlib import Path
+
+import pytest
+
+from min_fa3_demo_b200 import balancer as bal
+
+ROOT = Path(__file__).resolve().parents[1]
+spec = importlib.util.spec_from_file_location("bench_module", ROOT / "bench.py")
+bench = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(bench)
+
+
+def test_headline_workload_flops():
+    w = dict(bench.WORKLOAD)
+    assert (w["batch"], w["seqlen"], w["heads_q"], w["heads_k"], w["head_dim"], w["causal"]) == (4, 8192, 32, 8, 128, True)
+    fwd, bwd = bench.step_flops(w)
+    assert fwd == pytest.approx(2.199e12, rel=1e-3)
+    assert fwd + bwd == pytest.approx(7.697e12, rel=1e-3)
+    w["causal"] = False
+    fwd, bwd = bench.step_flops(w)
+    assert fwd + bwd == pytest.approx(1.539e13, rel=1e-3)
+
+
+def test_varlen_lengths_fill_exactly_and_respect_the_clip():
+    lens = bench.varlen_lengths()
+    assert sum(lens) == 65536 and min(lens) >= 1 and max(lens) <= 32768
+    assert (len(lens), max(lens), min(lens)) == (34, 7731, 128)     # the seed-0 realisation
+    assert lens == bench.varlen_lengths()                            # deterministic
+    assert any(n % 128 for n in lens), "lengths are meant to be ragged"
+
+
+def test_ring_varlen_documents_place_on_eight_ranks():
+    lengths = bal.sample_mixture_lengths(0, target_tokens=131072)
+    lengths[-1] -= sum(lengths) - 131072
+    assert sum(lengths) == 131072 and all(n % 256 == 0 and n > 0 for n in lengths)
+    plan = bal.assign_hierarchical_rings(lengths, 8, True)
+    assert plan.feasible
+    assert sum(plan.rank_tokens) == 131072
+    for rank in range(8):
+        lens, cu = bal.local_layout(plan, rank)
+        assert cu[-1] == plan.rank_tokens[rank] and all(n % 128 == 0 for n in lens)
