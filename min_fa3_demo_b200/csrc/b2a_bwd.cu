@@ -184,7 +184,7 @@ int b2a_bwd(const b2a_bwd_args* a, void* cuda_stream) {
         pre.lse_batch_stride = static_cast<long long>(a->heads_q) * a->seqlen_q;
     }
     {
-        dim3 grid((lay.padded_q + 7) / 8, a->heads_q);
+        dim3 grid((lay.padded_q + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp), a->heads_q);
         bwd_preprocess_kernel<<<grid, 256, 0, stream>>>(pre);
         B2A_CUDA_OK(cudaGetLastError());
     }
@@ -410,7 +410,7 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
         pre.padded_q = a->total_q;
         pre.lse_head_stride = a->total_q;
         pre.lse_batch_stride = 0;
-        dim3 pgrid((a->total_q + 7) / 8, a->heads_q);
+        dim3 pgrid((a->total_q + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp), a->heads_q);
         bwd_preprocess_kernel<<<pgrid, 256, 0, stream>>>(pre);
         B2A_CUDA_OK(cudaGetLastError());
 

@@ -1044,66 +1044,88 @@ struct BwdPreParams {
     long long lse_batch_stride;
 };
 
+constexpr int kPreRowsPerWarp = 4;   // rows per warp: their loads are all in flight together
+
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const BwdPreParams p) {
-    // grid: (padded_q / 8, heads_q); 8 warps per CTA, one padded row per warp.
+    // grid: (ceil(padded_q / 32), heads_q); 8 warps per CTA, kPreRowsPerWarp consecutive padded
+    // rows per warp.  The kernel is pure streaming (reads O and dO once); several rows per warp
+    // keep enough loads in flight to approach the memory bandwidth.
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int prow = blockIdx.x * 8 + warp;
+    const int prow0 = (blockIdx.x * 8 + warp) * kPreRowsPerWarp;
     const int h = blockIdx.y;
-    if (prow >= p.padded_q) return;
 
-    // Locate the document that owns this padded row.
-    int doc = -1, q_begin = 0, q_len = 0, pad_begin = 0;
-    if (p.cu_seqlens_q == nullptr) {
-        const int per = ((p.seqlen_q + 127) / 128) * 128;
-        doc = prow / per;
-        pad_begin = doc * per;
-        q_begin = doc * p.seqlen_q;
-        q_len = p.seqlen_q;
-        if (doc >= p.batch) doc = -1;
-    } else {
-        // Binary search over padded begins (monotone in doc).
-        int lo = 0, hi = p.batch - 1;
-        while (lo < hi) {
-            int mid = (lo + hi + 1) >> 1;
-            if (bwd_padded_begin(p.cu_seqlens_q[mid], mid) <= prow) lo = mid; else hi = mid - 1;
-        }
-        doc = lo;
-        q_begin = p.cu_seqlens_q[doc];
-        q_len = p.cu_seqlens_q[doc + 1] - q_begin;
-        pad_begin = bwd_padded_begin(q_begin, doc);
-        if (prow < pad_begin) doc = -1;
-    }
-    const int r = prow - pad_begin;
-    const long long out_idx = static_cast<long long>(h) * p.padded_q + prow;
-    float d = 0.f;
-    float l2 = INFINITY;
-    if (doc >= 0 && r < q_len) {
-        const long long tok = static_cast<long long>(q_begin) + r;
-        const long long base = (tok * p.heads_q + h) * kHeadDim + lane * 4;
-        const uint2 ov = *reinterpret_cast<const uint2*>(p.o + base);
-        const uint2 gv = *reinterpret_cast<const uint2*>(p.dout + base);
-        const float o0 = __uint_as_float(ov.x << 16), o1 = __uint_as_float(ov.x & 0xFFFF0000u);
-        const float o2 = __uint_as_float(ov.y << 16), o3 = __uint_as_float(ov.y & 0xFFFF0000u);
-        const float g0 = __uint_as_float(gv.x << 16), g1 = __uint_as_float(gv.x & 0xFFFF0000u);
-        const float g2 = __uint_as_float(gv.y << 16), g3 = __uint_as_float(gv.y & 0xFFFF0000u);
-        d = o0 * g0 + o1 * g1 + o2 * g2 + o3 * g3;
+    uint2 ov[kPreRowsPerWarp], gv[kPreRowsPerWarp];
+    long long lse_idx[kPreRowsPerWarp];
+    bool valid[kPreRowsPerWarp];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, off);
-        long long lse_idx;
+    for (int i = 0; i < kPreRowsPerWarp; ++i) {
+        const int prow = prow0 + i;
+        valid[i] = false;
+        lse_idx[i] = 0;
+        ov[i] = make_uint2(0u, 0u);
+        gv[i] = make_uint2(0u, 0u);
+        if (prow >= p.padded_q) continue;
+        // Locate the document that owns this padded row.
+        int doc = -1, q_begin = 0, q_len = 0, pad_begin = 0;
         if (p.cu_seqlens_q == nullptr) {
-            lse_idx = static_cast<long long>(doc) * p.lse_batch_stride +
-                      static_cast<long long>(h) * p.lse_head_stride + r;
+            const int per = ((p.seqlen_q + 127) / 128) * 128;
+            doc = prow / per;
+            pad_begin = doc * per;
+            q_begin = doc * p.seqlen_q;
+            q_len = p.seqlen_q;
+            if (doc >= p.batch) doc = -1;
         } else {
-            lse_idx = static_cast<long long>(h) * p.lse_head_stride + tok;
+            // Binary search over padded begins (monotone in doc).
+            int lo = 0, hi = p.batch - 1;
+            while (lo < hi) {
+                int mid = (lo + hi + 1) >> 1;
+                if (bwd_padded_begin(p.cu_seqlens_q[mid], mid) <= prow) lo = mid; else hi = mid - 1;
+            }
+            doc = lo;
+            q_begin = p.cu_seqlens_q[doc];
+            q_len = p.cu_seqlens_q[doc + 1] - q_begin;
+            pad_begin = bwd_padded_begin(q_begin, doc);
+            if (prow < pad_begin) doc = -1;
         }
-        const float l = p.lse[lse_idx];
-        l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+        const int r = prow - pad_begin;
+        if (doc >= 0 && r < q_len) {
+            valid[i] = true;
+            const long long tok = static_cast<long long>(q_begin) + r;
+            const long long base = (tok * p.heads_q + h) * kHeadDim + lane * 4;
+            ov[i] = *reinterpret_cast<const uint2*>(p.o + base);
+            gv[i] = *reinterpret_cast<const uint2*>(p.dout + base);
+            if (p.cu_seqlens_q == nullptr) {
+                lse_idx[i] = static_cast<long long>(doc) * p.lse_batch_stride +
+                             static_cast<long long>(h) * p.lse_head_stride + r;
+            } else {
+                lse_idx[i] = static_cast<long long>(h) * p.lse_head_stride + tok;
+            }
+        }
     }
-    if (lane == 0) {
-        p.lse2[out_idx] = l2;
-        p.dpsum[out_idx] = d;
+#pragma unroll
+    for (int i = 0; i < kPreRowsPerWarp; ++i) {
+        const int prow = prow0 + i;
+        if (prow >= p.padded_q) continue;
+        float d = 0.f;
+        float l2 = INFINITY;
+        if (valid[i]) {
+            const float o0 = __uint_as_float(ov[i].x << 16), o1 = __uint_as_float(ov[i].x & 0xFFFF0000u);
+            const float o2 = __uint_as_float(ov[i].y << 16), o3 = __uint_as_float(ov[i].y & 0xFFFF0000u);
+            const float g0 = __uint_as_float(gv[i].x << 16), g1 = __uint_as_float(gv[i].x & 0xFFFF0000u);
+            const float g2 = __uint_as_float(gv[i].y << 16), g3 = __uint_as_float(gv[i].y & 0xFFFF0000u);
+            d = o0 * g0 + o1 * g1 + o2 * g2 + o3 * g3;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, off);
+            const float l = p.lse[lse_idx[i]];
+            l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+        }
+        if (lane == 0) {
+            const long long out_idx = static_cast<long long>(h) * p.padded_q + prow;
+            p.lse2[out_idx] = l2;
+            p.dpsum[out_idx] = d;
+        }
     }
 }
 
