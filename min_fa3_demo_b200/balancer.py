@@ -12,7 +12,7 @@ holds ``length / G`` tokens and, thanks to the zigzag split, ``compute / G`` of 
 The search itself is this repository's own and much simpler than the reference's Pareto beam
 search: longest-processing-time greedy over all legal (size, start) candidates with a
 lexicographic (compute peak, token peak, communication) objective, followed by single-document
-re-placement moves until no move improves the objective.  It is a host-side planner off the
+re-placement moves, then moves of two documents at once, until no move improves the objective.  It is a host-side planner off the
 timed path; placements are legal and deterministic, and balance quality is tested against
 recorded results of the reference planner on the same inputs.
 """
@@ -173,6 +173,38 @@ def assign_hierarchical_rings(lengths: Sequence[int], world_size: int, is_causal
             placement[i] = best
             apply(i, best, +1.0)
 
+        moves_box = [0]
+
+        def pair_moves() -> bool:
+            cur = _objective(compute, tokens, comm[0], avg_c, avg_t, ctol, ttol, True)
+            movable = [i for i in order if len(candidates[i]) > 1]
+            for a_pos, i in enumerate(movable):
+                for k in movable[a_pos + 1:]:
+                    ci, ck = placement[i], placement[k]
+                    apply(i, ci, -1.0)
+                    apply(k, ck, -1.0)
+                    best, best_obj = None, cur
+                    for cand_i in candidates[i]:
+                        apply(i, cand_i, +1.0)
+                        for cand_k in candidates[k]:
+                            if cand_i == ci and cand_k == ck:
+                                continue
+                            apply(k, cand_k, +1.0)
+                            obj = _objective(compute, tokens, comm[0], avg_c, avg_t, ctol, ttol, True)
+                            apply(k, cand_k, -1.0)
+                            if obj[:3] < best_obj[:3]:
+                                best, best_obj = (cand_i, cand_k), obj
+                        apply(i, cand_i, -1.0)
+                    if best is not None:
+                        placement[i], placement[k] = best
+                        apply(i, best[0], +1.0)
+                        apply(k, best[1], +1.0)
+                        moves_box[0] += 2
+                        return True          # back to the (cheaper) single-move pass
+                    apply(i, ci, +1.0)
+                    apply(k, ck, +1.0)
+            return False
+
         # Local repair: move one document at a time while (violations, communication) improve.
         moves = 0
         for _ in range(max_repair_iterations):
@@ -194,9 +226,14 @@ def assign_hierarchical_rings(lengths: Sequence[int], world_size: int, is_causal
                     moves += 1
                     improved = True
             if not improved:
-                break
+                # Single moves are exhausted: try moving two documents at once (typically two
+                # equally long documents leaving a wide ring for two narrower ones side by side,
+                # which a single move cannot do without breaking the balance).
+                improved = pair_moves()
+                if not improved:
+                    break
         final = _objective(compute, tokens, comm[0], avg_c, avg_t, ctol, ttol, True)
-        return final, placement, compute, tokens, moves
+        return final, placement, compute, tokens, moves_box[0] + moves
 
     # Two starting points: communication-first inside the tolerances, and balance-first (which
     # the repair pass then thins out); keep whichever ends with the better objective.

@@ -61,12 +61,12 @@ def test_placement_is_legal_ordered_deterministic_and_balanced(case):
     # per-rank accounting is consistent
     assert sum(plan.rank_tokens) == sum(lengths)
     assert sum(plan.rank_compute) == pytest.approx(sum(bal.attention_compute(l, causal) for l in lengths))
-    # quality: feasible whenever the reference planner is, without excessive extra communication
+    # quality: feasible whenever the reference planner is, with at most 1.3x its communication volume
     if case["ref_feasible"]:
         assert plan.feasible
         assert plan.compute_deviation <= plan.compute_balance_tolerance + 1e-9
         assert plan.token_deviation <= plan.token_balance_tolerance + 1e-9
-    assert sum(plan.rank_communication) <= 2.2 * case["ref_communication"] + 1.0
+    assert sum(plan.rank_communication) <= 1.3 * case["ref_communication"] + 1.0
 
 
 def test_mixture_sampler_and_local_layout():
