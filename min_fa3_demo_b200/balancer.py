@@ -4,7 +4,7 @@ Same contract as the reference planner ``balancer.assign_hierarchical_rings``
 (``balancer/load_balancer.py:902-1085``): every document gets a ring of 1/2/4/8 consecutive
 ranks starting at a multiple of the ring size ("buddy" rings); a causal document may only use
 ring size G > 1 when ``length % (256 * G) == 0`` (``load_balancer.py:121-131``: both zigzag
-halves of every member stay 128-row aligned); the result lists the documents sorted by
+halves of every member stay 128-row aligned), a non-causal one when ``length % (128 * G) == 0``; the result lists the documents sorted by
 ``(-ring_size, ring_start, original index)`` (``load_balancer.py:1053-1060``), which is the
 order the context-parallel kernels require (ring sizes non-increasing).  Each ring member
 holds ``length / G`` tokens and, thanks to the zigzag split, ``compute / G`` of the work.
@@ -89,7 +89,11 @@ def eligible_ring_sizes(length: int, world_size: int, is_causal: bool) -> List[i
         if is_causal:
             if g == 1 or length % (256 * g) == 0:
                 out.append(g)
-        elif length % g == 0:
+        elif g == 1 or length % (128 * g) == 0:
+            # The reference accepts any length divisible by the ring size here
+            # (balancer/load_balancer.py:121-131), but its launch contract wants every member's
+            # shard to be a multiple of 128 rows; asking for that already in the planner keeps every
+            # plan launchable.
             out.append(g)
     return out
 

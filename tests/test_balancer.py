@@ -18,7 +18,8 @@ def test_eligible_ring_sizes_follow_the_reference_rule():
     assert bal.eligible_ring_sizes(2048, 8, True) == [1, 2, 4, 8]
     assert bal.eligible_ring_sizes(1024, 8, True) == [1, 2, 4]
     assert bal.eligible_ring_sizes(768, 8, True) == [1]
-    assert bal.eligible_ring_sizes(768, 4, False) == [1, 2, 4]
+    assert bal.eligible_ring_sizes(768, 4, False) == [1, 2]          # shards must stay multiples of 128 rows
+    assert bal.eligible_ring_sizes(1024, 4, False) == [1, 2, 4]
     assert bal.eligible_ring_sizes(4096, 2, True) == [1, 2]
 
 
@@ -81,3 +82,30 @@ def test_mixture_sampler_and_local_layout():
         assert all(l % 128 == 0 for l in lens)
         total += cu[-1]
     assert total == sum(lengths)
+
+
+# --------------------------------------------------------------------------------------
+# Property test: whatever the lengths, a plan is legal (the launch-time metadata rules of the
+# context-parallel entry points) and accounts for every token and every unit of work.
+# --------------------------------------------------------------------------------------
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+
+@settings(max_examples=40, deadline=None)
+@given(lengths=st.lists(st.integers(min_value=1, max_value=96).map(lambda n: n * 256), min_size=1, max_size=10),
+       world=st.sampled_from([2, 4, 8]), causal=st.booleans())
+def test_random_inputs_give_legal_plans(lengths, world, causal):
+    plan = bal.assign_hierarchical_rings(lengths, world, causal)
+    assert sorted(plan.global_lengths) == sorted(lengths)
+    assert sorted(plan.original_indices) == list(range(len(lengths)))
+    keys = [(-g, s, i) for g, s, i in zip(plan.ring_sizes, plan.ring_starts, plan.original_indices)]
+    assert keys == sorted(keys)                                   # non-increasing ring size, then start
+    for length, g, s in zip(plan.global_lengths, plan.ring_sizes, plan.ring_starts):
+        assert g in bal.eligible_ring_sizes(length, world, causal)
+        assert s % g == 0 and 0 <= s and s + g <= world
+        assert (length // g) % 128 == 0 and (not causal or g == 1 or (length // g // 2) % 128 == 0)
+    assert sum(plan.rank_tokens) == sum(lengths)
+    assert sum(plan.rank_compute) == pytest.approx(sum(bal.attention_compute(n, causal) for n in lengths))
+    for rank in range(world):
+        lens, cu = bal.local_layout(plan, rank)
+        assert cu[-1] == plan.rank_tokens[rank]
