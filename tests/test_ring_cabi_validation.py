@@ -56,3 +56,27 @@ def test_valid_metadata_passes_validation():
     # The metadata is accepted; the call then stops at the device query (no GPU) or at the
     # workspace-size check (GPU present) -- in both cases before anything is launched.
     assert rc in (_cabi.B2A_ERR_CUDA, _cabi.B2A_ERR_WORKSPACE_TOO_SMALL, _cabi.B2A_ERR_UNSUPPORTED_DEVICE), (rc, msg)
+
+
+# --------------------------------------------------------------------------------------
+# Planner <-> launcher contract: every plan the placement planner produces passes the native
+# metadata validation on every rank (checked without a GPU: the call stops at the device query
+# or at the workspace-size check, never at "invalid argument").
+# --------------------------------------------------------------------------------------
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+from min_fa3_demo_b200 import balancer as bal  # noqa: E402
+
+
+@settings(max_examples=25, deadline=None)
+@given(lengths=st.lists(st.integers(min_value=1, max_value=64).map(lambda n: n * 256), min_size=1, max_size=8),
+       world=st.sampled_from([2, 4, 8]), causal=st.booleans())
+def test_planner_output_is_accepted_by_the_launcher(lengths, world, causal):
+    plan = bal.assign_hierarchical_rings(lengths, world, causal)
+    cap = max(plan.rank_tokens)
+    cap = ((cap + 127) // 128) * 128
+    for rank in range(world):
+        _, cu = bal.local_layout(plan, rank)
+        rc, msg = call(cu=cu, glens=plan.global_lengths, sizes=plan.ring_sizes, starts=plan.ring_starts,
+                       world=world, rank=rank, cap=max(cap, 128), causal=int(causal))
+        assert rc != _cabi.B2A_ERR_INVALID_ARGUMENT, (rank, msg)

@@ -63,3 +63,25 @@ def test_host_vectors_are_checked():
     with pytest.raises(RuntimeError, match=r"ring_starts_host must have shape \[B\]"):
         ring._validate_ring_metadata(q, arena, i32(0, 512), i32(0, 512), i32(512), i32(1), i32(0, 0),
                                      4, 0, True, 512, 512)
+
+
+# Planner output always passes the host-side validation of the Python entry points.
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+from min_fa3_demo_b200 import balancer as bal  # noqa: E402
+
+
+@settings(max_examples=25, deadline=None)
+@given(lengths=st.lists(st.integers(min_value=1, max_value=64).map(lambda n: n * 256), min_size=1, max_size=8),
+       world=st.sampled_from([2, 4, 8]), causal=st.booleans())
+def test_planner_output_passes_python_validation(lengths, world, causal):
+    plan = bal.assign_hierarchical_rings(lengths, world, causal)
+    cap = ((max(plan.rank_tokens) + 127) // 128) * 128
+    for rank in range(world):
+        lens, cu = bal.local_layout(plan, rank)
+        q = torch.empty(cu[-1], 2, 128, dtype=torch.bfloat16)
+        arena = torch.empty(world * cap, 2, 128, dtype=torch.bfloat16)
+        got = ring._validate_ring_metadata(q, arena, i32(*cu), i32(*cu), i32(*plan.global_lengths),
+                                           i32(*plan.ring_sizes), i32(*plan.ring_starts), world, rank, causal,
+                                           max(max(lens), 1), max(max(lens), 1))
+        assert got == cap
