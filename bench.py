@@ -3,11 +3,16 @@
     python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
     python bench.py --impl reference --steps K --warmup W    # the reference's CPU attention
 
-One step is one forward + backward pass over the workload.  At every N the workload is
-benchmark configuration 2 per GPU (BSHD, causal, B=4, S=8192, QH=32, KVH=8, d=128, bf16 N(0,1)
-from a fixed seed): each rank owns an independent batch, there is no data-path collective,
-scaling is weak.  Printed numbers use the causal-discounted algorithmic FLOPs
-``14 * QH * D * sum_docs L(L+1)/2`` per step (forward 4x, backward 10x).
+One step is one forward + backward pass over the workload.  At every N the headline workload
+is benchmark configuration 2 per GPU (BSHD, causal, B=4, S=8192, QH=32, KVH=8, d=128, bf16
+N(0,1) from a fixed seed): each rank owns an independent batch, there is no data-path
+collective, scaling is weak.  For N >= 2 the same run then executes the path that shards --
+context parallel, benchmark configuration 4: one 131,072-token causal sequence zigzag-sharded
+over the N ranks with the K/V exchange inside the attention kernels -- times it with the
+reference's protocol, times the same problem on rank 0 alone (T(1)), checks every rank's
+results against fp32 PyTorch, and reports all of it as ``config.ring_cp`` (and as a JSON line
+of its own before the headline line).  Printed numbers use the causal-discounted algorithmic
+FLOPs ``14 * QH * D * sum_docs L(L+1)/2`` per step (forward 4x, backward 10x).
 
 The JSON line carries: ``value`` (whole-job TFLOPS with inputs resident in HBM, CUDA events,
 max over ranks), ``e2e`` (same metric from pinned host buffers to pinned host buffers through
@@ -307,6 +312,13 @@ def run_cuda_arm(args) -> None:
     h2d = sum(host[n].numel() * 2 for n in ("q", "k", "v", "dout"))
     d2h = sum(t.numel() * 2 for t in host_out.values())
 
+    # ---- context parallel on the same N ranks (N >= 2) -------------------------------------------
+    ring_cp = None
+    if world > 1 and not args.skip_ring:
+        del q, k, v, dout, pipeline
+        torch.cuda.empty_cache()
+        ring_cp = ring_cp_leg(args, rank, local_rank, world, dev, dist)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -350,9 +362,317 @@ def run_cuda_arm(args) -> None:
     traffic_file = ROOT / "profiles" / "bwd_kernel_traffic.json"
     if traffic_file.exists():
         line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get("dram_bytes_per_launch")
+    if ring_cp is not None:
+        # The path that shards: reported beside the replica headline (whose `value` stays the
+        # configuration-2 number at every N) and as a line of its own.
+        line["config"]["ring_cp"] = ring_cp
+        print(json.dumps({"record": "ring_cp", **ring_cp}), flush=True)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------
+# Context-parallel leg of the default multi-GPU run (benchmark configuration 4)
+# --------------------------------------------------------------------------------------
+def _zigzag_positions(world: int, rank: int, local: int, device) -> torch.Tensor:
+    """Global positions of a rank's [front | back] shard: chunks r and 2W-1-r of 2W equal chunks."""
+    half = local // 2
+    ar = torch.arange(half, device=device)
+    if world == 1:
+        return torch.arange(local, device=device)
+    return torch.cat([ar + rank * half, ar + (2 * world - 1 - rank) * half])
+
+
+def _dense_rows(qs, k, v, qpos, kpos, dout=None, low_precision=False):
+    """Checker, plain PyTorch on the GPU: causal attention of a few query rows ``qs [R, QH, 128]``
+    over keys ``k, v [T, KVH, 128]`` with explicit positions (key j visible to row i when
+    ``kpos[j] <= qpos[i]``).  fp32 throughout, or -- ``low_precision`` -- with bf16 scores,
+    probabilities and products, the yardstick of the acceptance rule.  Returns ``out [R, QH, 128]``,
+    ``lse [QH, R]`` and, with ``dout``, the gradients with respect to qs, k and v."""
+    dt = torch.bfloat16 if low_precision else torch.float32
+    group = qs.size(1) // k.size(1)
+    leaves = [t.detach().to(dt).requires_grad_(dout is not None) for t in (qs, k, v)]
+    q_, k_, v_ = leaves
+    rows, kvh, t = qs.size(0), k.size(1), k.size(0)
+    qg = q_.view(rows, kvh, group, 128)
+    scores = torch.einsum("rhgd,thd->hgrt", qg, k_).float() * (128 ** -0.5)
+    scores = scores.masked_fill((kpos[None, :] > qpos[:, None])[None, None], float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1).reshape(kvh * group, rows)
+    probs = torch.softmax(scores, dim=-1).to(dt)
+    out = torch.einsum("hgrt,thd->rhgd", probs, v_).reshape(rows, kvh * group, 128)
+    grads = None
+    if dout is not None:
+        grads = torch.autograd.grad(out, leaves, dout.to(dt))
+    return out.detach().float(), lse.detach(), grads
+
+
+def _bound(e_low_precision: float) -> float:
+    # acceptance rule: 2x the error of a bf16 PyTorch attention, never tighter than half a bf16 ulp at 1
+    return 2.0 * max(e_low_precision, 2.0 ** -9)
+
+
+def ring_cp_leg(args, rank: int, local_rank: int, world: int, dev, dist) -> dict:
+    """Context parallel on all N ranks of the run: one 131,072-token causal sequence (QH 32, KVH 8,
+    d 128), zigzag-sharded, K/V pulled over NVLink inside the attention launches, dK/dV added into
+    the owner's accumulators.  Timing follows the reference's protocol
+    (ring_test/benchmark_topology_forward.py:382-411, .../benchmark_ring_backward.py:413-446):
+    CUDA events around forward and backward separately, per-iteration maximum over ranks, mean of
+    the maxima; the accumulator zeroing + barrier before each backward is outside the timed part.
+    In the same run rank 0 alone times the same 131,072-token problem on one GPU (T(1)), and every
+    rank checks its results against a plain fp32 PyTorch computation on the GPU: O / LSE / dQ of
+    sampled local rows of the full-size problem (all heads), and every output of a 2,048-token
+    zigzag problem (all heads)."""
+    import min_fa3_op
+    from min_fa3_demo_b200 import _cabi
+    from min_fa3_demo_b200.ring import dkv_accum_numel
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    lib = _cabi.load()
+    qh, kvh, tokens = 32, 8, args.ring_tokens
+    local = tokens // world
+    cap = local
+    sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    comm = args.ring_comm_sm
+    warm = 3
+    steps = max(3, min(args.steps, 10))
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    arena_k = torch.zeros(world * cap, kvh, 128, dtype=torch.bfloat16, device=dev)
+    arena_v = torch.zeros_like(arena_k)
+    rk = min_fa3_op.TKParallelTensor(arena_k, local_rank=local_rank, local_world_size=world, multicast=False)
+    rv = min_fa3_op.TKParallelTensor(arena_v, local_rank=local_rank, local_world_size=world, multicast=False)
+    accum = dkv_accum_numel(kvh, cap, 1)
+    acc_k = min_fa3_op.TKParallelTensor([accum], torch.float32, local_rank, world, False)
+    acc_v = min_fa3_op.TKParallelTensor([accum], torch.float32, local_rank, world, False)
+    done = min_fa3_op.TKParallelTensor([1], torch.int32, local_rank, world, False)
+
+    def run_ring(q, k, v, dout, glen):
+        """One forward + backward of a single zigzag-sharded document of ``glen`` global tokens."""
+        n = q.size(0)
+        cu = torch.tensor([0, n], dtype=torch.int32)
+        cud = cu.to(dev)
+        meta = dict(global_seqlens_host=torch.tensor([glen], dtype=torch.int32),
+                    ring_sizes_host=torch.tensor([world], dtype=torch.int32),
+                    ring_starts_host=torch.tensor([0], dtype=torch.int32))
+        arena_k[rank * cap:rank * cap + n] = k
+        arena_v[rank * cap:rank * cap + n] = v
+        barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ev[0].record()
+        out, lse = min_fa3_op.forward_varlen_mega_ring(
+            q, rk.data_, rv.data_, cud, cud, n, n, True, cu_seqlens_q_host=cu, cu_seqlens_k_host=cu,
+            remote_k=rk, remote_v=rv, num_comp_sm=sm - comm, num_comm_sm=comm, return_lse=True, **meta)
+        ev[1].record()
+        acc_k.data_.zero_()
+        acc_v.data_.zero_()
+        done.data_.zero_()
+        barrier()
+        ev[2].record()
+        dq, dk, dv = min_fa3_op.backward_varlen_mega_ring(
+            dout, q, rk.data_, rv.data_, out, lse, cud, cud, n, n, cu_seqlens_q_host=cu, cu_seqlens_k_host=cu,
+            remote_k=rk, remote_v=rv, remote_dk_accum=acc_k, remote_dv_accum=acc_v, remote_dkv_completion=done,
+            num_comp_sm=sm - comm, num_comm_sm=comm, **meta)
+        ev[3].record()
+        torch.cuda.synchronize()
+        times = torch.tensor([ev[0].elapsed_time(ev[1]), ev[2].elapsed_time(ev[3])], device=dev)
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        return (out, lse, dq, dk, dv), times
+
+    # ---- timed runs at full size --------------------------------------------------------
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    q = torch.randn(local, qh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    k = torch.randn(local, kvh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn(local, kvh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    dout = torch.randn(local, qh, 128, device=dev, generator=gen).to(torch.bfloat16)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    fwd_ms, bwd_ms, results = [], [], None
+    for it in range(warm + steps):
+        if it == warm:
+            sampler.mark_begin()
+        results, t = run_ring(q, k, v, dout, tokens)
+        if it >= warm:
+            fwd_ms.append(t[0].item())
+            bwd_ms.append(t[1].item())
+    sampler.mark_end()
+    clocks_ring = sampler.stop() if rank == 0 else None
+    status_ok = True
+    try:
+        min_fa3_op.check_last_status()
+    except RuntimeError as exc:
+        status_ok = False
+        print(f"[rank {rank}] ring leg device status: {exc}", file=sys.stderr, flush=True)
+
+    # ---- parity, full size: sampled local rows against fp32 PyTorch over the gathered K/V -----
+    out, lse, dq, dk, dv = results
+    gk = torch.empty(world, local, kvh, 128, dtype=torch.bfloat16, device=dev)
+    gv = torch.empty_like(gk)
+    dist.all_gather_into_tensor(gk, k)      # checker plumbing, not the product's data path
+    dist.all_gather_into_tensor(gv, v)
+    kpos = torch.cat([_zigzag_positions(world, r, local, dev) for r in range(world)])
+    qpos_all = _zigzag_positions(world, rank, local, dev)
+    half = local // 2
+    picks = sorted({0, 1, 127, 128, half - 1, half, half + 1, local - 129, local - 128, local - 1,
+                    *[(104729 * (j + 1) * (rank + 3)) % local for j in range(22)]})
+    rows = torch.tensor(picks, device=dev)
+    kf, vf = gk.view(-1, kvh, 128), gv.view(-1, kvh, 128)
+    ref_o, ref_l, ref_g = _dense_rows(q[rows], kf, vf, qpos_all[rows], kpos, dout[rows])
+    low_o, _low_l, low_g = _dense_rows(q[rows], kf, vf, qpos_all[rows], kpos, dout[rows], low_precision=True)
+    full = {
+        "rows_per_rank": len(picks),
+        "o_err": (out[rows].float() - ref_o).abs().max().item(),
+        "o_bound": _bound((low_o - ref_o).abs().max().item()),
+        "lse_err": (lse[:, rows] - ref_l).abs().max().item(), "lse_bound": 1e-3,
+        "dq_err": (dq[rows].float() - ref_g[0]).abs().max().item(),
+        "dq_bound": _bound((low_g[0].float() - ref_g[0]).abs().max().item()),
+    }
+    del gk, gv, kf, vf, ref_o, ref_l, ref_g, low_o, low_g
+
+    # ---- parity, 2,048-token zigzag problem: every output, all heads ----------------------------
+    small_tokens = max(2048, 256 * world)
+    s_local = small_tokens // world
+    gen_s = torch.Generator(device=dev).manual_seed(77)           # same global problem on every rank
+    qg = torch.randn(small_tokens, qh, 128, device=dev, generator=gen_s).to(torch.bfloat16)
+    kg = torch.randn(small_tokens, kvh, 128, device=dev, generator=gen_s).to(torch.bfloat16)
+    vg = torch.randn(small_tokens, kvh, 128, device=dev, generator=gen_s).to(torch.bfloat16)
+    dg = torch.randn(small_tokens, qh, 128, device=dev, generator=gen_s).to(torch.bfloat16)
+    mine = _zigzag_positions(world, rank, s_local, dev)
+    (so, sl, sdq, sdk, sdv), _ = run_ring(qg[mine].contiguous(), kg[mine].contiguous(), vg[mine].contiguous(),
+                                          dg[mine].contiguous(), small_tokens)
+    pos = torch.arange(small_tokens, device=dev)
+    ref_o, ref_l, ref_g = _dense_rows(qg, kg, vg, pos, pos, dg)
+    low_o, _l, low_g = _dense_rows(qg, kg, vg, pos, pos, dg, low_precision=True)
+    small = {"tokens": small_tokens,
+             "o_err": (so.float() - ref_o[mine]).abs().max().item(),
+             "o_bound": _bound((low_o - ref_o).abs().max().item()),
+             "lse_err": (sl - ref_l[:, mine]).abs().max().item(), "lse_bound": 1e-3}
+    for name, got, idx in (("dq", sdq, 0), ("dk", sdk, 1), ("dv", sdv, 2)):
+        small[f"{name}_err"] = (got.float() - ref_g[idx][mine]).abs().max().item()
+        small[f"{name}_bound"] = _bound((low_g[idx].float() - ref_g[idx]).abs().max().item())
+    try:
+        min_fa3_op.check_last_status()
+    except RuntimeError as exc:
+        status_ok = False
+        print(f"[rank {rank}] ring parity device status: {exc}", file=sys.stderr, flush=True)
+
+    def passes(rec):
+        return all(rec[key] <= rec[key.replace("_err", "_bound")] for key in rec if key.endswith("_err"))
+    ok_local = status_ok and passes(full) and passes(small)
+    flag = torch.tensor([0 if ok_local else 1], device=dev, dtype=torch.int32)
+    dist.all_reduce(flag)
+    # worst error / bound ratio over ranks, per quantity
+    keys = [("full", key) for key in full if key.endswith("_err")] + [("small", key) for key in small if key.endswith("_err")]
+    ratios = torch.tensor([(full if w == "full" else small)[key] / (full if w == "full" else small)[key.replace("_err", "_bound")]
+                           for w, key in keys], device=dev)
+    dist.all_reduce(ratios, op=dist.ReduceOp.MAX)
+
+    # ---- peer copy probe: every rank pulls its neighbour's K slice with the library's copy kernel --
+    probe_bytes = local * kvh * 128 * 2
+    landing = torch.empty(local, kvh, 128, dtype=torch.bfloat16, device=dev)
+    src = rk.raw_ptrs_[(rank + 1) % world] + ((rank + 1) % world) * cap * kvh * 256
+    probe = {}
+    for blocks in (8, 32, 128):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        reps = 4
+        lib.b2a_peer_copy(ctypes.c_void_p(landing.data_ptr()), ctypes.c_void_p(src), probe_bytes, blocks, None, stream)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            lib.b2a_peer_copy(ctypes.c_void_p(landing.data_ptr()), ctypes.c_void_p(src), probe_bytes, blocks, None, stream)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        probe[f"{blocks}_ctas_gbs"] = probe_bytes / (t.item() * 1e-3) / 1e9
+    del landing
+
+    # ---- T(1): the same problem on rank 0 alone ------------------------------------------------------
+    barrier()
+    t1 = torch.zeros(3, device=dev)
+    clocks_t1 = None
+    if rank == 0:
+        del q, k, v, dout, results, out, lse, dq, dk, dv
+        torch.cuda.empty_cache()
+        gen1 = torch.Generator(device=dev).manual_seed(4242)
+        q1 = torch.randn(tokens, qh, 128, device=dev, generator=gen1).to(torch.bfloat16)
+        k1 = torch.randn(tokens, kvh, 128, device=dev, generator=gen1).to(torch.bfloat16)
+        v1 = torch.randn(tokens, kvh, 128, device=dev, generator=gen1).to(torch.bfloat16)
+        d1 = torch.randn(tokens, qh, 128, device=dev, generator=gen1).to(torch.bfloat16)
+        cu1 = torch.tensor([0, tokens], dtype=torch.int32)
+        cu1d = cu1.to(dev)
+        sampler1 = ClockSampler(local_rank)
+        sampler1.start()
+        f_ms, b_ms = [], []
+        for it in range(1 + 2):
+            if it == 1:
+                sampler1.mark_begin()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record()
+            o1, l1 = min_fa3_op.forward_varlen(q1, k1, v1, cu1d, cu1d, tokens, tokens, True, cu_seqlens_q_host=cu1,
+                                               cu_seqlens_k_host=cu1, return_lse=True)
+            ev[1].record()
+            min_fa3_op.backward_varlen(d1, q1, k1, v1, o1, l1, cu1d, cu1d, tokens, tokens, True)
+            ev[2].record()
+            torch.cuda.synchronize()
+            if it >= 1:
+                f_ms.append(ev[0].elapsed_time(ev[1]))
+                b_ms.append(ev[1].elapsed_time(ev[2]))
+        sampler1.mark_end()
+        clocks_t1 = sampler1.stop()
+        t1 = torch.tensor([statistics.mean(f_ms), statistics.mean(b_ms), 1.0], device=dev)
+        del q1, k1, v1, d1, o1, l1
+        torch.cuda.empty_cache()
+    barrier()
+
+    fm, bm = statistics.mean(fwd_ms), statistics.mean(bwd_ms)
+    vis = tokens * (tokens + 1) / 2
+    f_flops, b_flops = 4.0 * qh * 128 * vis, 10.0 * qh * 128 * vis
+    ingress = (world - 1) * local * kvh * 128 * 2 * 2         # rank 0 sees every other shard: K and V
+    burst, sustained, peak_kind = measured_peaks()
+    rec = {
+        "workload": f"ring_cp_causal_S{tokens}_QH{qh}_KVH{kvh}_D128", "n_gpus": world, "gpus_active": world,
+        "parallelism": f"cp{world} zigzag ring, K/V pulled over NVLink in-kernel, dK/dV added into the owner's "
+                       "accumulators over NVLink",
+        "steps": steps, "warmup": warm,
+        "timing": "CUDA events, forward and backward separately, per-iteration max over ranks, mean; the "
+                  "accumulator zeroing + barrier before each backward is not timed (reference protocol)",
+        "fwd_ms": fm, "bwd_ms": bm, "ms_per_step": fm + bm,
+        "tflops_per_gpu": (f_flops + b_flops) / ((fm + bm) * 1e-3) / 1e12 / world,
+        "fwd_tflops_per_gpu": f_flops / (fm * 1e-3) / 1e12 / world,
+        "bwd_tflops_per_gpu": b_flops / (bm * 1e-3) / 1e12 / world,
+        "pct_of_bf16_peak_burst": 100.0 * (f_flops + b_flops) / ((fm + bm) * 1e-3) / 1e12 / world / burst,
+        "copy_ctas": comm,
+        "kv_ingress_bytes_rank0_fwd": ingress, "kv_ingress_gbs": ingress / (fm * 1e-3) / 1e9,
+        "peer_copy_probe": {"bytes": probe_bytes, "what": "b2a_peer_copy of the neighbour rank's K slice, all "
+                            "ranks at once, max over ranks", **probe},
+        "parity": {"pass": flag.item() == 0, "device_status_ok": status_ok,
+                   "rule": "max-abs error <= 2x the error of the same computation with bf16 scores/probabilities "
+                           "(both against fp32 PyTorch on the GPU); LSE <= 1e-3",
+                   "worst_err_over_bound": {f"{w}.{key[:-4]}": ratios[i].item() for i, (w, key) in enumerate(keys)},
+                   "rank0_full_size_sampled_rows": full, "rank0_small_problem": small},
+    }
+    if rank == 0:
+        t1f, t1b = t1[0].item(), t1[1].item()
+        mhz_n = (clocks_ring or {}).get("sm_mhz")
+        mhz_1 = (clocks_t1 or {}).get("sm_mhz")
+        rec.update({
+            "t1_fwd_ms": t1f, "t1_bwd_ms": t1b, "t1_ms": t1f + t1b,
+            "t1_what": "same 131,072-token causal problem through forward_varlen / backward_varlen on rank 0 "
+                       "alone, measured in this run (1 warm-up + 2 timed steps)",
+            "sm_mhz": {"ring": mhz_n, "t1": mhz_1}, "clocks_ring": clocks_ring, "clocks_t1": clocks_t1,
+            "efficiency": (t1f + t1b) / (world * (fm + bm)),
+            "efficiency_fwd": t1f / (world * fm), "efficiency_bwd": t1b / (world * bm),
+            "efficiency_clock_normalised": ((t1f + t1b) * mhz_1) / (world * (fm + bm) * mhz_n)
+            if mhz_1 and mhz_n else None,
+        })
+    return rec
 
 
 # --------------------------------------------------------------------------------------
@@ -440,8 +760,10 @@ def run_ring_workload(args) -> None:
         arena_v[rank * cap:rank * cap + local] = v
         rk = min_fa3_op.TKParallelTensor(arena_k, local_rank=local_rank, local_world_size=world, multicast=False)
         rv = min_fa3_op.TKParallelTensor(arena_v, local_rank=local_rank, local_world_size=world, multicast=False)
-        acc_k = min_fa3_op.TKParallelTensor([kvh * cap * 128], torch.float32, local_rank, world, False)
-        acc_v = min_fa3_op.TKParallelTensor([kvh * cap * 128], torch.float32, local_rank, world, False)
+        from min_fa3_demo_b200.ring import dkv_accum_numel
+        accum = dkv_accum_numel(kvh, cap, len(glens))
+        acc_k = min_fa3_op.TKParallelTensor([accum], torch.float32, local_rank, world, False)
+        acc_v = min_fa3_op.TKParallelTensor([accum], torch.float32, local_rank, world, False)
         done = min_fa3_op.TKParallelTensor([1], torch.int32, local_rank, world, False)
         meta = dict(global_seqlens_host=torch.tensor(glens, dtype=torch.int32),
                     ring_sizes_host=torch.tensor(sizes, dtype=torch.int32),
@@ -698,6 +1020,8 @@ def main() -> None:
                              "allgather = comparison baseline, NCCL all_gather of K/V + plain varlen attention + "
                              "NCCL reduce_scatter of dK/dV")
     parser.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
+    parser.add_argument("--skip-ring", action="store_true",
+                        help="N >= 2: skip the context-parallel leg (131,072-token ring) of the default run")
     parser.add_argument("--e2e-head-groups", type=int, default=2,
                         help="chunks per batch element in the host-buffer pipeline (must divide the KV heads)")
     parser.add_argument("--skip-cpu-baseline", action="store_true", help="skip the CPU baseline leg")

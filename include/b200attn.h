@@ -63,6 +63,15 @@ typedef struct b2a_fwd_args {
     float softmax_scale;        /* 0 = 1/sqrt(head_dim) */
     void* workspace;            /* device scratch, 16-byte aligned */
     size_t workspace_bytes;
+    /* Ring step (all NULL / 0 otherwise): prefetch_blocks extra CTAs of the same launch first copy
+     * prefetch_bytes (a multiple of 16) from prefetch_src_k / _v -- normally another rank's K / V
+     * reached through a peer mapping -- to prefetch_dst_k / _v, then join the attention work. */
+    const void* prefetch_src_k;
+    const void* prefetch_src_v;
+    void* prefetch_dst_k;
+    void* prefetch_dst_v;
+    size_t prefetch_bytes;
+    int32_t prefetch_blocks;
 } b2a_fwd_args;
 
 /* Scratch needed by b2a_fwd for these sizes. */
@@ -73,8 +82,11 @@ size_t b2a_fwd_workspace_bytes(int32_t batch, int32_t total_q, int32_t is_varlen
  * Replaces `forward` (bindings.cpp:240) and `forward_varlen` (bindings.cpp:280)
  * of the reference, including its varlen scheduler-metadata kernel
  * (csrc/min_fa3_varlen_prepare_scheduler.cu:214); with merge_running = 1 it is
- * the compute half of `forward_varlen_ring`
- * (csrc/min_fa3_varlen_ring_bindings.cu:231).
+ * `forward_varlen_ring` (csrc/min_fa3_varlen_ring_bindings.cu:231): attention merged into
+ * the running out/lse on CTAs [0, grid_blocks) and, with the prefetch_* fields set, the copy
+ * of the next source rank's K/V on CTAs [grid_blocks, grid_blocks + prefetch_blocks) of the
+ * same launch (the reference's compute + communication kernel,
+ * include/min_fa3_varlen_ring_launch.h:217).
  */
 int b2a_fwd(const b2a_fwd_args* args, void* cuda_stream);
 
@@ -100,6 +112,7 @@ int b2a_fwd(const b2a_fwd_args* args, void* cuda_stream);
  * cleared on the stream by every call; the rest keeps the previous call's contents.  Two
  * calls that may overlap on the GPU (different streams, no dependency) race on it -- order
  * them, or use b2a_fwd with separate workspaces.
+ * Status: b2a_check_status(NULL, stream) reads the status word of the built-in scratch.
  */
 int b2a_fwd_noalloc(const b2a_fwd_args* args, void* cuda_stream);
 
@@ -298,9 +311,23 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* args, void* cuda_stream);
  * this workspace wrote.  Returns B2A_OK, or B2A_ERR_DEVICE_STATUS with the
  * decoded status in b2a_last_error() (for example a bounded wait that ran out).
  * No counterpart in the reference, whose device-side waits are unbounded
- * (include/mega_ring_semaphore.cuh:69-80).
+ * (include/mega_ring_semaphore.cuh:69-80).  workspace == NULL reads the status
+ * word of the scratch built into the library, i.e. of the last b2a_fwd_noalloc
+ * call on the current device.
  */
 int b2a_check_status(const void* workspace, void* cuda_stream);
+
+/*
+ * Limit, in nanoseconds, of every bounded device-side wait (mbarriers, K/V block
+ * flags, deterministic-order counters) of launches made after the call; the
+ * cross-rank completion wait that ends b2a_ring_bwd gets ten times this value.
+ * Default 2 s; accepted range 1 us .. 4 s; 0 restores the default.  Process-wide.
+ * A wait that runs out never traps or hangs: the kernel records
+ * (wait site, CTA) in the status word, drains and returns, and b2a_check_status
+ * reports it.  No counterpart in the reference (include/mega_ring_semaphore.cuh:69-80
+ * spins without a limit).
+ */
+int b2a_set_wait_timeout_ns(uint64_t nanoseconds);
 
 /* ------------------------------------------------------------------------- */
 /* Kernel timing                                                              */

@@ -46,6 +46,12 @@ class FwdArgs(Structure):
         ("softmax_scale", c_float),
         ("workspace", c_void_p),
         ("workspace_bytes", c_size_t),
+        ("prefetch_src_k", c_void_p),
+        ("prefetch_src_v", c_void_p),
+        ("prefetch_dst_k", c_void_p),
+        ("prefetch_dst_v", c_void_p),
+        ("prefetch_bytes", c_size_t),
+        ("prefetch_blocks", c_int32),
     ]
 
 
@@ -172,6 +178,7 @@ SIGNATURES = {
     "b2a_ring_bwd_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "b2a_ring_bwd": (c_int32, [POINTER(RingBwdArgs), c_void_p]),
     "b2a_check_status": (c_int32, [c_void_p, c_void_p]),
+    "b2a_set_wait_timeout_ns": (c_int32, [ctypes.c_uint64]),
     "b2a_profile_enable": (c_int32, [c_int32]),
     "b2a_profile_read": (c_int32, [c_int32, POINTER(c_float), c_int32]),
 }

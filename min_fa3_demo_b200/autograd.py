@@ -126,20 +126,26 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
 class _RingFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, ring: "RingAttention", cu, cu_host, max_len: int, meta):
-        ring._load_kv(k, v)
+        generation = ring._load_kv(k, v)
         out, lse = _op.forward_varlen_mega_ring(
             q, ring.arena_k.data_, ring.arena_v.data_, cu, cu, max_len, max_len, ring.is_causal,
             cu_seqlens_q_host=cu_host, cu_seqlens_k_host=cu_host, remote_k=ring.arena_k, remote_v=ring.arena_v,
             num_comp_sm=ring.num_comp_sm, num_comm_sm=ring.num_comm_sm, return_lse=True, **meta)
-        ctx.save_for_backward(q, out, lse, cu)
+        ctx.save_for_backward(q, k, v, out, lse, cu)
         ctx.ring, ctx.cu_host, ctx.max_len, ctx.meta = ring, cu_host, max_len, meta
-        ctx.kv_rows = k.size(0)
+        ctx.kv_rows, ctx.generation = k.size(0), generation
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, out, lse, cu = ctx.saved_tensors
+        q, k, v, out, lse, cu = ctx.saved_tensors
         ring: RingAttention = ctx.ring
+        if ring._generation != ctx.generation:
+            # Another forward has used the arena since this call's forward (several layers or
+            # micro-batches share the object, or activation checkpointing re-ran a forward): put
+            # this call's K/V back.  Every rank sees the same sequence of calls, so all of them
+            # take this branch together (it contains barriers).
+            ctx.generation = ring._load_kv(k, v)
         ring._reset_backward_buffers()
         dq, dk, dv = _op.backward_varlen_mega_ring(
             dout.contiguous(), q, ring.arena_k.data_, ring.arena_v.data_, out, lse, cu, cu, ctx.max_len, ctx.max_len,
@@ -159,13 +165,15 @@ class RingAttention:
     counter, all peer-visible.  ``__call__`` takes this rank's packed shard ``q, k, v``
     ``[T_local, H, 128]`` in the placement's document order (zigzag ``[front | back]`` halves for
     causal rings) with the placement metadata, and is differentiable.  Calls must be made by all
-    ranks together (they contain barriers); the arena is reused, so a second forward must not
-    start before the backward of the first has finished — the usual one-layer-at-a-time order of
-    training code.
+    ranks together, in the same order (they contain barriers).  One object may serve many layers
+    or micro-batches: the arena holds the K/V of the latest forward, and a backward whose K/V has
+    been overwritten since copies its saved K/V back first (one extra local copy and two
+    barriers); with one object per layer that never happens.  ``max_documents`` bounds the
+    number of documents per call (it sizes the fp32 dK/dV accumulators).
     """
 
     def __init__(self, rank_kv_capacity: int, heads_k: int, *, is_causal: bool = True, num_comm_sm: int = 8,
-                 device: Optional[torch.device] = None, group=None):
+                 device: Optional[torch.device] = None, group=None, max_documents: int = 64):
         import torch.distributed as dist
 
         self.dist = dist
@@ -186,16 +194,22 @@ class RingAttention:
             return _op.TKParallelTensor(t, local_rank=local_rank, local_world_size=self.world, multicast=False)
         self.arena_k = parallel((self.world * self.cap, heads_k, 128), torch.bfloat16)
         self.arena_v = parallel((self.world * self.cap, heads_k, 128), torch.bfloat16)
-        self.acc_k = parallel((heads_k * self.cap * 128,), torch.float32)
-        self.acc_v = parallel((heads_k * self.cap * 128,), torch.float32)
+        from .ring import dkv_accum_numel
+        self.max_documents = int(max_documents)
+        accum = dkv_accum_numel(heads_k, self.cap, self.max_documents)
+        self.acc_k = parallel((accum,), torch.float32)
+        self.acc_v = parallel((accum,), torch.float32)
         self.done = parallel((1,), torch.int32)
+        self._generation = 0        # counts arena loads; identical on every rank
 
     def _barrier(self) -> None:
         torch.cuda.current_stream(self.device).synchronize()
         if self.world > 1:
             self.dist.barrier(self.group)
 
-    def _load_kv(self, k: torch.Tensor, v: torch.Tensor) -> None:
+    def _load_kv(self, k: torch.Tensor, v: torch.Tensor) -> int:
+        """Copies this rank's K/V into its arena slice (between two barriers) and returns the
+        arena generation that now holds them."""
         if k.size(0) > self.cap:
             raise RuntimeError(f"local K/V has {k.size(0)} rows, the arena holds {self.cap} per rank")
         self._barrier()                       # nobody still reads the arena of a previous call
@@ -203,6 +217,8 @@ class RingAttention:
         self.arena_k.data_[lo:lo + k.size(0)].copy_(k.detach())
         self.arena_v.data_[lo:lo + v.size(0)].copy_(v.detach())
         self._barrier()                       # every rank's slice is in place
+        self._generation += 1
+        return self._generation
 
     def _reset_backward_buffers(self) -> None:
         self.acc_k.data_.zero_()
@@ -212,6 +228,9 @@ class RingAttention:
 
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, local_lengths: Sequence[int],
                  global_lengths: Sequence[int], ring_sizes: Sequence[int], ring_starts: Sequence[int]) -> torch.Tensor:
+        if len(local_lengths) > self.max_documents:
+            raise RuntimeError(f"{len(local_lengths)} documents in one call, but the accumulators were sized "
+                               f"for max_documents={self.max_documents}")
         cu_list: List[int] = [0]
         for n in local_lengths:
             cu_list.append(cu_list[-1] + int(n))

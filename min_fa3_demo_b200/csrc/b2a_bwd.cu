@@ -4,7 +4,6 @@
 #include "b2a_ring_host.cuh"
 
 #include <cmath>
-#include <cstdlib>
 #include <cstring>
 
 namespace b2a {
@@ -18,12 +17,8 @@ constexpr size_t kBwdSmemBytes = sizeof(BwdShared);
 // 512 bytes) within about the size of L2.  Measured on B200 (QH=32, KVH=8): at S=8192 all 8 heads
 // together are best (B=2: 1.9 GB of DRAM traffic per launch against 5.3 GB with 3 heads and 3.8 GB
 // with 1; 2.33 / 2.52 / 2.42 ms); on one 131,072-token sequence 1 or 2 heads are best (329 / 331 ms
-// against 350 ms with all 8).  The environment variable B2A_BWD_SG_HEADS overrides the choice.
+// against 350 ms with all 8).
 int pick_sg_heads(int heads_q, int heads_k, long long q_rows) {
-    if (const char* env = getenv("B2A_BWD_SG_HEADS")) {
-        const int v = atoi(env);
-        if (v >= 1) return v < heads_k ? v : heads_k;
-    }
     const long long per_head = static_cast<long long>(heads_q / heads_k) * (q_rows > 0 ? q_rows : 1) * 512;
     const long long budget = 160ll << 20;
     long long n = budget / per_head;
@@ -68,18 +63,18 @@ BwdLayout bwd_layout(int batch, int seqlen_q, int total_q, int total_k, int head
     return l;
 }
 
-int configure_bwd_kernel(const DeviceInfo& dev) {
-    static bool done[64] = {};
-    if (!done[dev.device]) {
-        if (static_cast<size_t>(dev.max_smem_optin) < kBwdSmemBytes) {
-            return fail(B2A_ERR_UNSUPPORTED_DEVICE, "device offers %d bytes of shared memory, need %zu",
-                        dev.max_smem_optin, kBwdSmemBytes);
-        }
-        B2A_CUDA_OK(cudaFuncSetAttribute(bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kBwdSmemBytes)));
-        done[dev.device] = true;
-    }
+int set_bwd_smem_attribute() {
+    B2A_CUDA_OK(cudaFuncSetAttribute(bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kBwdSmemBytes)));
     return B2A_OK;
+}
+
+int configure_bwd_kernel(const DeviceInfo& dev) {
+    if (static_cast<size_t>(dev.max_smem_optin) < kBwdSmemBytes) {
+        return fail(B2A_ERR_UNSUPPORTED_DEVICE, "device offers %d bytes of shared memory, need %zu",
+                    dev.max_smem_optin, kBwdSmemBytes);
+    }
+    return once_per_device(dev.device, 2, set_bwd_smem_attribute);
 }
 
 }  // namespace
@@ -215,7 +210,7 @@ int b2a_bwd(const b2a_bwd_args* a, void* cuda_stream) {
     p.padded_q = lay.padded_q;
     p.scale = scale;
     p.scale_log2 = scale * kLog2e;
-    p.timeout_ns = kDefaultTimeoutNs;
+    p.timeout_ns = wait_timeout_ns();
 
     p.sg_heads = pick_sg_heads(a->heads_q, a->heads_k, varlen ? a->total_q : a->seqlen_q);
     long long work_items;
@@ -353,7 +348,7 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
     for (int d : plan.doc_order) {
         const RingDoc& doc = plan.docs[d];
         const int g = doc.ring_size, r = doc.ring_rank, hb = doc.half_len / kTileN;
-        const int halves = g == 1 ? 1 : 2;
+        const int halves = ring_halves(causal, g);
         for (int s = 0; s < g; ++s) {
             for (int hf = 0; hf < halves; ++hf) {
                 const int ck = g == 1 ? 0 : (hf == 0 ? s : 2 * g - 1 - s);
@@ -441,7 +436,7 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
         p.padded_q = a->total_q;
         p.scale = scale;
         p.scale_log2 = scale * kLog2e;
-        p.timeout_ns = kDefaultTimeoutNs;
+        p.timeout_ns = wait_timeout_ns();
         p.ring_docs = reinterpret_cast<const RingDoc*>(ws + lay.docs_off);
         p.ring_work = reinterpret_cast<const int4*>(ws + lay.work_off);
         p.comm_tasks = reinterpret_cast<const int2*>(ws + lay.tasks_off);
@@ -464,12 +459,8 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
         p.done_ctas = &hdr->reserved;
         p.world = world;
 
-        static bool configured[64] = {};
-        if (!configured[dev.device]) {
-            B2A_CUDA_OK(cudaFuncSetAttribute(bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kRingBwdSmemBytes)));
-            configured[dev.device] = true;
-        }
+        rc = configure_bwd_kernel(dev);
+        if (rc != B2A_OK) return rc;
         const int comm = p.comm_task_count > 0 ? a->num_comm_sm : 0;
         const int grid = a->num_comp_sm + comm;
         profile_mark(B2A_KERNEL_BWD, false, stream);
@@ -497,7 +488,7 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
     }
 
     // Every rank has added its contributions once this rank's counter reaches the world size.
-    ring_wait_kernel<<<1, 1, 0, stream>>>(a->completion_peer[rank], world, &hdr->status, 20000000000ull);
+    ring_wait_kernel<<<1, 1, 0, stream>>>(a->completion_peer[rank], world, &hdr->status, completion_timeout_ns());
     B2A_CUDA_OK(cudaGetLastError());
     if (a->local_total_k > 0) {
         for (int which = 0; which < 2; ++which) {

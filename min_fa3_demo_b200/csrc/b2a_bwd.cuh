@@ -197,7 +197,7 @@ __device__ __forceinline__ BwdWork bwd_decode_work(const BwdParams& p, int w) {
         // Global chunk indices: key chunk ck, query chunks cq of the two local halves.
         const int ck = g == 1 ? 0 : (hf == 0 ? s : 2 * g - 1 - s);
         int first[2] = {0, 0}, count[2] = {0, 0};
-        const int halves = g == 1 ? 1 : 2;
+        const int halves = ring_halves(p.causal, g);
         for (int h = 0; h < halves; ++h) {
             if (!p.causal) {
                 count[h] = hb;
@@ -1027,7 +1027,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 
 // ---------------------------------------------------------------------------------------
 // Preprocess: one warp per query row.  D = sum_d dO * O, LSE2 = LSE * log2(e) with -inf and
-// padding rows mapped to +inf (their P becomes exactly 0).  Also zeroes dq_accum.
+// padding rows mapped to +inf (their P becomes exactly 0).
 // ---------------------------------------------------------------------------------------
 struct BwdPreParams {
     const __nv_bfloat16* o;

@@ -12,22 +12,22 @@ namespace {
 constexpr size_t kFwdSmemBytes = sizeof(FwdShared) + 1024;   // + slack for 1 KiB alignment
 
 template <bool kMerge>
-int configure_fwd_kernel(const DeviceInfo& dev) {
-    static bool done[64][2] = {};
-    if (!done[dev.device][kMerge ? 1 : 0]) {
-        if (static_cast<size_t>(dev.max_smem_optin) < kFwdSmemBytes) {
-            return fail(B2A_ERR_UNSUPPORTED_DEVICE, "device offers %d bytes of shared memory, need %zu",
-                        dev.max_smem_optin, kFwdSmemBytes);
-        }
-        B2A_CUDA_OK(cudaFuncSetAttribute(fwd_kernel<kMerge>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kFwdSmemBytes)));
-        done[dev.device][kMerge ? 1 : 0] = true;
-    }
+int set_fwd_smem_attribute() {
+    B2A_CUDA_OK(cudaFuncSetAttribute(fwd_kernel<kMerge>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kFwdSmemBytes)));
     return B2A_OK;
 }
 
 }  // namespace
+
+int configure_fwd_kernel(const DeviceInfo& dev, bool merge) {
+    if (static_cast<size_t>(dev.max_smem_optin) < kFwdSmemBytes) {
+        return fail(B2A_ERR_UNSUPPORTED_DEVICE, "device offers %d bytes of shared memory, need %zu",
+                    dev.max_smem_optin, kFwdSmemBytes);
+    }
+    return merge ? once_per_device(dev.device, 1, set_fwd_smem_attribute<true>)
+                 : once_per_device(dev.device, 0, set_fwd_smem_attribute<false>);
+}
 
 }  // namespace b2a
 
@@ -60,6 +60,17 @@ int b2a_fwd(const b2a_fwd_args* a, void* cuda_stream) {
                     "BSHD sizes must satisfy total = batch * seqlen");
     }
     B2A_REQUIRE(a->grid_blocks >= 0, "grid_blocks must be >= 0, got %d", a->grid_blocks);
+    const bool prefetch = a->prefetch_bytes != 0;
+    if (prefetch) {
+        B2A_REQUIRE(a->prefetch_src_k && a->prefetch_src_v && a->prefetch_dst_k && a->prefetch_dst_v,
+                    "prefetch source and destination pointers must not be NULL when prefetch_bytes > 0");
+        B2A_REQUIRE(a->prefetch_bytes % 16 == 0, "prefetch_bytes must be a multiple of 16, got %zu", a->prefetch_bytes);
+        B2A_REQUIRE(a->prefetch_blocks > 0, "prefetch_blocks must be positive when prefetch_bytes > 0, got %d",
+                    a->prefetch_blocks);
+        const uintptr_t align = reinterpret_cast<uintptr_t>(a->prefetch_src_k) | reinterpret_cast<uintptr_t>(a->prefetch_src_v) |
+                                reinterpret_cast<uintptr_t>(a->prefetch_dst_k) | reinterpret_cast<uintptr_t>(a->prefetch_dst_v);
+        B2A_REQUIRE((align & 0xF) == 0, "prefetch buffers must be 16-byte aligned");
+    }
     B2A_REQUIRE(a->workspace != nullptr && (reinterpret_cast<uintptr_t>(a->workspace) & 0xF) == 0,
                 "workspace must be a 16-byte aligned device pointer");
     const size_t need = b2a_fwd_workspace_bytes(a->batch, a->total_q, varlen ? 1 : 0);
@@ -105,7 +116,7 @@ int b2a_fwd(const b2a_fwd_args* a, void* cuda_stream) {
     p.scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / std::sqrt(static_cast<float>(kHeadDim));
     p.scale_log2 = p.scale * kLog2e;
     p.merge = a->merge_running ? 1 : 0;
-    p.timeout_ns = kDefaultTimeoutNs;
+    p.timeout_ns = wait_timeout_ns();
 
     long long work_items;
     if (varlen) {
@@ -128,14 +139,24 @@ int b2a_fwd(const b2a_fwd_args* a, void* cuda_stream) {
     int grid = a->grid_blocks > 0 ? a->grid_blocks : dev.sm_count;
     if (work_items < grid) grid = static_cast<int>(work_items);
     if (grid < 1) grid = 1;
+    p.num_comp = grid;
+    if (prefetch) {
+        // Copy CTAs ride in the same launch behind the compute CTAs; neither kind waits for the other.
+        p.prefetch_src[0] = static_cast<const uint8_t*>(a->prefetch_src_k);
+        p.prefetch_src[1] = static_cast<const uint8_t*>(a->prefetch_src_v);
+        p.prefetch_dst[0] = static_cast<uint8_t*>(a->prefetch_dst_k);
+        p.prefetch_dst[1] = static_cast<uint8_t*>(a->prefetch_dst_v);
+        p.prefetch_bytes = a->prefetch_bytes;
+        grid += a->prefetch_blocks;
+    }
 
     if (p.merge) {
-        rc = configure_fwd_kernel<true>(dev);
+        rc = configure_fwd_kernel(dev, true);
         if (rc != B2A_OK) return rc;
         profile_mark(B2A_KERNEL_FWD, false, stream);
         fwd_kernel<true><<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(map_q, map_k, map_v, p);
     } else {
-        rc = configure_fwd_kernel<false>(dev);
+        rc = configure_fwd_kernel(dev, false);
         if (rc != B2A_OK) return rc;
         profile_mark(B2A_KERNEL_FWD, false, stream);
         fwd_kernel<false><<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(map_q, map_k, map_v, p);
@@ -159,6 +180,8 @@ namespace {
 // this array resident until the process exits.
 constexpr size_t kNoAllocScratchBytes = 64 * 1024;
 static __device__ __align__(256) unsigned char g_fwd_noalloc_scratch[kNoAllocScratchBytes];
+
+}  // namespace
 
 // Device address of the array on each device.  The array's name is only a host-side handle
 // in host code; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
@@ -185,7 +208,6 @@ int noalloc_scratch_ptr(void** out) {
     return B2A_OK;
 }
 
-}  // namespace
 }  // namespace b2a
 
 extern "C" {

@@ -87,12 +87,17 @@ struct FwdParams {
     uint8_t* arena_k;                  // this rank's arena (the tensor maps of K/V cover it)
     uint8_t* arena_v;
     int* kv_flags;                     // per 128-row arena block: 1 once K and V have landed
+    // ---- ring step mode: CTAs [num_comp, gridDim.x) first copy two flat buffers (another rank's
+    // K and V) into local prefetch buffers, then join the attention work queue.  0 otherwise.
+    const uint8_t* prefetch_src[2];
+    uint8_t* prefetch_dst[2];
+    unsigned long long prefetch_bytes; // per buffer, a multiple of 16
 };
 
 // Placement of one document on its ring.  Lengths are in tokens, multiples of 128.
 struct RingDoc {
     int q_begin;        // first local token of the document on this rank
-    int half_len;       // local length / 2 for rings, local length for ring_size 1
+    int half_len;       // local length / 2 on a causal ring (zigzag halves), else the local length
     int ring_size;      // G
     int ring_rank;      // this rank's position in the ring (global rank - ring_start)
     int member_row[8];  // arena row of the document's slice on ring member s
@@ -131,15 +136,21 @@ struct __align__(1024) FwdShared {
     uint32_t abort_flag;
 };
 
-// Number of whole (unmasked) chunks a query half sees before its own chunk.  A chunk is
-// half_len tokens: zigzag rank r of a ring of G holds global chunks r (front) and 2G-1-r
-// (back); causally a query chunk sees every chunk with a smaller global index.
-__device__ __forceinline__ int ring_full_chunks(int causal, int ring_size, int ring_rank, int half) {
+// Pieces a member's shard is cut into: two zigzag halves on a causal ring, otherwise one.
+__host__ __device__ __forceinline__ int ring_halves(int causal, int ring_size) {
+    return (causal && ring_size > 1) ? 2 : 1;
+}
+
+// Number of whole (unmasked) chunks a query piece sees before its own chunk.  A chunk is
+// half_len tokens.  Causal: zigzag rank r of a ring of G holds global chunks r (front) and
+// 2G-1-r (back), and a query chunk sees every chunk with a smaller global index.  Without a
+// mask every member's shard is one chunk and all G of them are visible.
+__host__ __device__ __forceinline__ int ring_full_chunks(int causal, int ring_size, int ring_rank, int half) {
     if (causal) {
         if (ring_size == 1) return 0;
         return half == 0 ? ring_rank : 2 * ring_size - 1 - ring_rank;
     }
-    return ring_size == 1 ? 1 : 2 * ring_size;
+    return ring_size;
 }
 
 __device__ __forceinline__ FwdWork fwd_decode_work(const FwdParams& p, int w) {
@@ -235,16 +246,10 @@ __device__ __forceinline__ int ring_kv_row(const FwdParams& p, const FwdWork& wk
                 s = g - 1 - (k >> 1);
                 hf = k & 1;
             }
-        } else if (g == 1) {
-            s = 0;
-            hf = 0;
-        } else if (slot < 2) {
-            s = r;
-            hf = slot;
         } else {
-            const int k = slot - 2;
-            s = (r - 1 - (k >> 1) + g) % g;
-            hf = k & 1;
+            // no mask: the own shard first, then sources r-1, r-2, ... around the ring
+            s = (r - slot + g) % g;
+            hf = 0;
         }
     }
     *remote = (s != r);
@@ -334,6 +339,46 @@ __device__ __forceinline__ void ring_copy_role(const FwdParams& p, FwdShared& sh
     }
 }
 
+// Copy role of a ring-step CTA: two flat buffers (K, then V) are cut into 32 KiB pieces that
+// the copy CTAs take round-robin and move peer -> shared -> local with the same two-thread,
+// six-slot pipeline as above.  The last piece of a buffer may be shorter (still a multiple of 16).
+__device__ __forceinline__ void prefetch_copy_role(const FwdParams& p, FwdShared& sh, const WaitCtx& wctx,
+                                                   int warp, int lane) {
+    constexpr unsigned long long kSlotBytes = kTileBytes;
+    const uint32_t slot_base = smem_u32(&sh.q[0][0]);
+    const long long per_buf = static_cast<long long>((p.prefetch_bytes + kSlotBytes - 1) / kSlotBytes);
+    const long long first = static_cast<long long>(blockIdx.x) - p.num_comp;
+    const long long stride = static_cast<long long>(gridDim.x) - p.num_comp;
+    if ((warp != 9 && warp != 10) || lane != 0) return;
+    uint32_t it = 0;
+    bool ok = true;
+    for (long long t = first; t < 2 * per_buf && ok; t += stride, ++it) {
+        const int kv = t >= per_buf ? 1 : 0;
+        const unsigned long long off = static_cast<unsigned long long>(t - kv * per_buf) * kSlotBytes;
+        const unsigned long long left = p.prefetch_bytes - off;
+        const uint32_t bytes = static_cast<uint32_t>(left < kSlotBytes ? left : kSlotBytes);
+        const uint32_t slot = it % 6u;
+        if (warp == 9) {
+            ok = mbar_wait(wctx, smem_u32(&sh.comm_empty[slot]), ((it / 6u) & 1u) ^ 1u, 27);
+            if (!ok) break;
+            mbar_arrive_expect_tx(smem_u32(&sh.comm_full[slot]), bytes);
+            bulk_load_1d(slot_base + slot * static_cast<uint32_t>(kSlotBytes), p.prefetch_src[kv] + off, bytes,
+                         smem_u32(&sh.comm_full[slot]));
+        } else {
+            ok = mbar_wait(wctx, smem_u32(&sh.comm_full[slot]), (it / 6u) & 1u, 28);
+            if (!ok) break;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                         ::"l"(reinterpret_cast<uint64_t>(p.prefetch_dst[kv] + off)),
+                           "r"(slot_base + slot * static_cast<uint32_t>(kSlotBytes)), "r"(bytes)
+                         : "memory");
+            bulk_commit_group();
+            bulk_wait_group_read<0>();
+            mbar_arrive(smem_u32(&sh.comm_empty[slot]));
+        }
+    }
+    if (warp == 10) bulk_wait_group<0>();
+}
+
 template <bool kMerge>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -387,6 +432,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     // join the attention work queue like every other CTA.
     if (p.ring_docs != nullptr && static_cast<int>(blockIdx.x) >= p.num_comp && p.comm_task_count > 0) {
         ring_copy_role(p, sh, wctx, warp, lane);
+        __syncthreads();
+    }
+    if (p.prefetch_bytes != 0ull && static_cast<int>(blockIdx.x) >= p.num_comp) {
+        prefetch_copy_role(p, sh, wctx, warp, lane);
         __syncthreads();
     }
 

@@ -1,6 +1,7 @@
 // Host-side helpers: error text, device properties, tensor-map encoding, status read-back.
 #include "b2a_host.cuh"
 
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -47,6 +48,27 @@ int current_device_info(DeviceInfo* info) {
                     info->cc_major, info->cc_minor);
     }
     return B2A_OK;
+}
+
+namespace {
+std::atomic<uint32_t> g_wait_timeout_ns{kDefaultTimeoutNs};
+}  // namespace
+
+uint32_t wait_timeout_ns() { return g_wait_timeout_ns.load(std::memory_order_relaxed); }
+
+unsigned long long completion_timeout_ns() { return 10ull * wait_timeout_ns(); }
+
+int once_per_device(int device, int slot, int (*fn)()) {
+    static std::mutex mu;
+    static bool done[64][8] = {};
+    if (device < 0 || device >= 64 || slot < 0 || slot >= 8) {
+        return fail(B2A_ERR_CUDA, "device index %d out of range", device);
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[device][slot]) return B2A_OK;
+    const int rc = fn();
+    if (rc == B2A_OK) done[device][slot] = true;
+    return rc;
 }
 
 namespace {
@@ -152,13 +174,29 @@ int b2a_profile_read(int kernel, float* ms, int capacity) {
     return n;
 }
 
-int b2a_abi_version(void) { return 1; }
+int b2a_abi_version(void) { return 2; }
 
 const char* b2a_last_error(void) { return b2a::error_buffer(); }
 
+int b2a_set_wait_timeout_ns(uint64_t nanoseconds) {
+    using namespace b2a;
+    if (nanoseconds == 0) nanoseconds = kDefaultTimeoutNs;
+    B2A_REQUIRE(nanoseconds >= 1000 && nanoseconds <= kMaxTimeoutNs,
+                "wait timeout must be between 1000 ns and %u ns (0 restores the default), got %llu",
+                kMaxTimeoutNs, static_cast<unsigned long long>(nanoseconds));
+    g_wait_timeout_ns.store(static_cast<uint32_t>(nanoseconds), std::memory_order_relaxed);
+    return B2A_OK;
+}
+
 int b2a_check_status(const void* workspace, void* cuda_stream) {
     using namespace b2a;
-    B2A_REQUIRE(workspace != nullptr, "workspace must not be NULL");
+    if (workspace == nullptr) {
+        // The scratch of b2a_fwd_noalloc lives inside the library; its header is read the same way.
+        void* scratch = nullptr;
+        const int rc = noalloc_scratch_ptr(&scratch);
+        if (rc != B2A_OK) return rc;
+        workspace = scratch;
+    }
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
     WorkspaceHeader hdr{};
     B2A_CUDA_OK(cudaMemcpyAsync(&hdr, workspace, sizeof(hdr), cudaMemcpyDeviceToHost, stream));

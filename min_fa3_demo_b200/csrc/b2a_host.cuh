@@ -65,6 +65,24 @@ inline size_t max_entries(int batch, int total_tokens, int rows) {
 }
 
 constexpr uint32_t kDefaultTimeoutNs = 2000000000u;   // bounded device waits: 2 s
+constexpr uint32_t kMaxTimeoutNs = 4000000000u;       // the waits compare 32-bit nanosecond timers
+
+// Limit of every bounded device-side wait of launches made from now on (b2a_set_wait_timeout_ns).
+uint32_t wait_timeout_ns();
+// Limit of the cross-rank completion wait that ends the context-parallel backward: ten times
+// the limit above, because it covers the other ranks' whole backward launch and their launch skew.
+unsigned long long completion_timeout_ns();
+
+// Device address of the scratch array built into the library for b2a_fwd_noalloc (looked up
+// once per device with cudaGetSymbolAddress; defined beside the array in b2a_fwd.cu).
+int noalloc_scratch_ptr(void** out);
+
+// Runs `fn` once per (device, slot) under a lock; used for cudaFuncSetAttribute calls.
+// Returns fn's code the first time and B2A_OK afterwards.
+int once_per_device(int device, int slot, int (*fn)());
+
+// Raises the dynamic shared-memory limit of the forward kernel once per device (b2a_fwd.cu).
+int configure_fwd_kernel(const DeviceInfo& dev, bool merge);
 
 // Planner launch (b2a_plan.cu).  kind 0: forward items (256 query rows of a
 // document, cost = visible key blocks).  kind 1: backward items (128 key rows

@@ -145,17 +145,18 @@ int b2a_peer_copy(void* dst, const void* src, size_t bytes, int32_t num_blocks, 
     DeviceInfo dev{};
     int rc = current_device_info(&dev);
     if (rc != B2A_OK) return rc;
-    static bool configured[64] = {};
     const int smem = kCopySlots * kCopySlotBytes;
-    if (!configured[dev.device]) {
-        B2A_CUDA_OK(cudaFuncSetAttribute(peer_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        configured[dev.device] = true;
-    }
+    rc = once_per_device(dev.device, 3, [] {
+        B2A_CUDA_OK(cudaFuncSetAttribute(peer_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kCopySlots * kCopySlotBytes));
+        return static_cast<int>(B2A_OK);
+    });
+    if (rc != B2A_OK) return rc;
     const size_t chunks = (bytes + kCopySlotBytes - 1) / kCopySlotBytes;
     int grid = num_blocks;
     if (static_cast<size_t>(grid) > chunks) grid = static_cast<int>(chunks);
     peer_copy_kernel<<<grid, kCopyThreads, smem, static_cast<cudaStream_t>(cuda_stream)>>>(
-        static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), bytes, status, kDefaultTimeoutNs);
+        static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), bytes, status, wait_timeout_ns());
     B2A_CUDA_OK(cudaGetLastError());
     return B2A_OK;
 }

@@ -93,12 +93,9 @@ int b2a_ring_fwd(const b2a_ring_fwd_args* a, void* cuda_stream) {
     for (int d : plan.doc_order) {
         const RingDoc& doc = plan.docs[d];
         const int hb = doc.half_len / kTileN;
-        const int halves = doc.ring_size > 1 ? 2 : 1;
+        const int halves = ring_halves(causal, doc.ring_size);
         for (int h = 0; h < halves; ++h) {
-            int chunks;
-            if (causal) chunks = doc.ring_size == 1 ? 0 : (h == 0 ? doc.ring_rank : 2 * doc.ring_size - 1 - doc.ring_rank);
-            else chunks = doc.ring_size == 1 ? 1 : 2 * doc.ring_size;
-            const int n_full = chunks * hb;
+            const int n_full = ring_full_chunks(causal, doc.ring_size, doc.ring_rank, h) * hb;
             for (int pair = 0; pair * 2 < hb; ++pair) {
                 const int t_last = std::min(hb - 1, pair * 2 + 1);
                 entries.push_back({make_int4(d, h, pair, 0), n_full + (causal ? t_last + 1 : 0)});
@@ -161,7 +158,7 @@ int b2a_ring_fwd(const b2a_ring_fwd_args* a, void* cuda_stream) {
     p.scale = 1.0f / std::sqrt(static_cast<float>(kHeadDim));
     p.scale_log2 = p.scale * kLog2e;
     p.lse_head_stride = a->total_q;
-    p.timeout_ns = kDefaultTimeoutNs;
+    p.timeout_ns = wait_timeout_ns();
     p.ring_docs = reinterpret_cast<const RingDoc*>(ws + lay.docs_off);
     p.ring_work = reinterpret_cast<const int4*>(ws + lay.work_off);
     p.comm_tasks = reinterpret_cast<const int2*>(ws + lay.tasks_off);
@@ -180,12 +177,8 @@ int b2a_ring_fwd(const b2a_ring_fwd_args* a, void* cuda_stream) {
     int grid = a->num_comp_sm + comm;
     p.num_comp = a->num_comp_sm;
 
-    static bool configured[64] = {};
-    if (!configured[dev.device]) {
-        B2A_CUDA_OK(cudaFuncSetAttribute(fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kRingFwdSmemBytes)));
-        configured[dev.device] = true;
-    }
+    rc = configure_fwd_kernel(dev, false);
+    if (rc != B2A_OK) return rc;
     profile_mark(B2A_KERNEL_FWD, false, stream);
     fwd_kernel<false><<<grid, kFwdThreads, kRingFwdSmemBytes, stream>>>(map_q, map_k, map_v, p);
     profile_mark(B2A_KERNEL_FWD, true, stream);

@@ -62,7 +62,7 @@ inline int build_ring_plan(RingPlan* plan, int batch, int world, int rank, int c
         doc.q_begin = cu_seqlens_q_host[d];
         doc.ring_size = g;
         doc.ring_rank = member ? rank - start : 0;
-        doc.half_len = member ? (g > 1 ? llen / 2 : llen) : 0;
+        doc.half_len = member ? llen / ring_halves(causal, g) : 0;
         for (int j = 0; j < 8; ++j) doc.member_row[j] = 0;
         for (int j = 0; j < g; ++j) {
             doc.member_row[j] = (start + j) * cap + off[start + j];
@@ -77,8 +77,8 @@ inline int build_ring_plan(RingPlan* plan, int batch, int world, int rank, int c
     std::stable_sort(plan->doc_order.begin(), plan->doc_order.end(),
                      [&](int a, int b) { return global_seqlens[a] > global_seqlens[b]; });
     // Copy tasks in the order the attention loops consume remote chunks: for every document,
-    // sources r-1, r-2, ... around its ring; the front half always, the back half when a local
-    // query half can see it (always without a causal mask, else only for sources after r).
+    // sources r-1, r-2, ... around its ring.  Causal: the front half always, the back half only
+    // for sources after r (a local query half can see it).  Without a mask a shard is one chunk.
     for (int d : plan->doc_order) {
         const RingDoc& doc = plan->docs[d];
         const int g = doc.ring_size, r = doc.ring_rank, start = ring_starts[d];
@@ -87,7 +87,7 @@ inline int build_ring_plan(RingPlan* plan, int batch, int world, int rank, int c
             const int s = (r - i + g) % g;
             const int row0 = doc.member_row[s];
             for (int w = 0; w < hb; ++w) plan->comm_tasks.push_back(make_int2(start + s, row0 / 128 + w));
-            if (!causal || s > r) {
+            if (causal && s > r) {
                 for (int w = 0; w < hb; ++w) {
                     plan->comm_tasks.push_back(make_int2(start + s, (row0 + doc.half_len) / 128 + w));
                 }

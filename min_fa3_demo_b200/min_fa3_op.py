@@ -11,6 +11,7 @@ entry points still works (for CPU-side argument checks) but every compute call r
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import Optional, Tuple, Union
 
 import torch
@@ -30,6 +31,7 @@ __all__ = [
     "parallel_remote_load",
     "parallel_remote_load_vec",
     "_debug_resolve_launch_grid_shape",
+    "check_last_status",
 ]
 
 _INT32_MAX = 2**31 - 1
@@ -178,7 +180,9 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _call_fwd(q, k, v, out, lse, *, cu_q, cu_k, batch, seqlen_q, seqlen_k, heads_q, heads_k,
-              is_causal, merge_running=False, grid_blocks=0):
+              is_causal, merge_running=False, grid_blocks=0, prefetch=None):
+    """``prefetch``: optional ``(src_k_ptr, src_v_ptr, dst_k, dst_v, blocks)`` -- that many extra
+    CTAs of the launch copy ``dst_k.numel() * 2`` bytes from each source address first."""
     lib = _cabi.load()
     total_q = q.numel() // (heads_q * 128)
     total_k = k.numel() // (heads_k * 128)
@@ -196,6 +200,12 @@ def _call_fwd(q, k, v, out, lse, *, cu_q, cu_k, batch, seqlen_q, seqlen_k, heads
     args.grid_blocks = int(grid_blocks or 0)
     args.softmax_scale = 0.0
     args.workspace, args.workspace_bytes = ws.data_ptr(), nbytes
+    if prefetch is not None:
+        src_k, src_v, dst_k, dst_v, blocks = prefetch
+        args.prefetch_src_k, args.prefetch_src_v = src_k, src_v
+        args.prefetch_dst_k, args.prefetch_dst_v = dst_k.data_ptr(), dst_v.data_ptr()
+        args.prefetch_bytes = dst_k.numel() * dst_k.element_size()
+        args.prefetch_blocks = int(blocks)
     with torch.cuda.device(q.device):
         _cabi.check(lib.b2a_fwd(ctypes.byref(args), _stream_ptr(q.device)))
     return ws
@@ -234,6 +244,33 @@ def check_device_status(workspace: torch.Tensor) -> None:
                                      _stream_ptr(workspace.device)))
 
 
+# Scratch of the most recent call of each entry point on this thread.  Keeping the tensor alive
+# keeps the 16-byte header with the device status word readable after the call has returned.
+_LAST = threading.local()
+
+
+def _remember_workspace(entry_point: str, workspace: torch.Tensor) -> None:
+    table = getattr(_LAST, "workspaces", None)
+    if table is None:
+        table = _LAST.workspaces = {}
+    table[entry_point] = workspace
+
+
+def check_last_status(entry_point: Optional[str] = None) -> None:
+    """Synchronise and raise ``RuntimeError`` if the most recent call of ``entry_point`` (e.g.
+    ``"forward"``, ``"backward_varlen_mega_ring"``; default: every entry point) made on this
+    thread left a device-side error: a bounded wait that ran out, or a failed device check.
+    The kernels never trap or hang on such an error; they record it and return, and this is how
+    the host learns of it (the reference's device waits are unbounded and report nothing,
+    include/mega_ring_semaphore.cuh:69-80)."""
+    table = getattr(_LAST, "workspaces", None) or {}
+    names = [entry_point] if entry_point is not None else list(table)
+    for name in names:
+        ws = table.get(name)
+        if ws is not None:
+            check_device_status(ws)
+
+
 # --------------------------------------------------------------------------------------
 # public API
 # --------------------------------------------------------------------------------------
@@ -262,9 +299,10 @@ def forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool, 
 
     out = torch.empty_like(q)
     lse = torch.empty((q.size(0), q.size(2), q.size(1)), dtype=torch.float32, device=q.device)
-    _call_fwd(q, k, v, out, lse, cu_q=None, cu_k=None, batch=q.size(0), seqlen_q=q.size(1),
-              seqlen_k=k.size(1), heads_q=q.size(2), heads_k=k.size(2), is_causal=is_causal,
-              grid_blocks=manual or 0)
+    ws = _call_fwd(q, k, v, out, lse, cu_q=None, cu_k=None, batch=q.size(0), seqlen_q=q.size(1),
+                   seqlen_k=k.size(1), heads_q=q.size(2), heads_k=k.size(2), is_causal=is_causal,
+                   grid_blocks=manual or 0)
+    _remember_workspace("forward", ws)
     if return_lse:
         return out, lse
     return out
@@ -316,9 +354,10 @@ def forward_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
 
     out = torch.empty_like(q)
     lse = torch.empty((q.size(1), q.size(0)), dtype=torch.float32, device=q.device)
-    _call_fwd(q, k, v, out, lse, cu_q=cu_seqlens_q, cu_k=cu_seqlens_k, batch=batch,
-              seqlen_q=max_seqlen_q, seqlen_k=max_seqlen_k, heads_q=q.size(1), heads_k=k.size(1),
-              is_causal=is_causal, grid_blocks=manual or 0)
+    ws = _call_fwd(q, k, v, out, lse, cu_q=cu_seqlens_q, cu_k=cu_seqlens_k, batch=batch,
+                   seqlen_q=max_seqlen_q, seqlen_k=max_seqlen_k, heads_q=q.size(1), heads_k=k.size(1),
+                   is_causal=is_causal, grid_blocks=manual or 0)
+    _remember_workspace("forward_varlen", ws)
     if return_lse:
         return out, lse
     return out
@@ -356,9 +395,10 @@ def backward(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
     dq = _grad_output(dq, q, "dq")
     dk = _grad_output(dk, k, "dk")
     dv = _grad_output(dv, v, "dv")
-    _call_bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_q=None, cu_k=None, batch=q.size(0),
-              seqlen_q=q.size(1), seqlen_k=k.size(1), heads_q=q.size(2), heads_k=k.size(2),
-              is_causal=is_causal, deterministic=deterministic)
+    ws = _call_bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_q=None, cu_k=None, batch=q.size(0),
+                   seqlen_q=q.size(1), seqlen_k=k.size(1), heads_q=q.size(2), heads_k=k.size(2),
+                   is_causal=is_causal, deterministic=deterministic)
+    _remember_workspace("backward", ws)
     return dq, dk, dv
 
 
@@ -399,10 +439,11 @@ def backward_varlen(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: tor
     dq = _grad_output(dq, q, "dq")
     dk = _grad_output(dk, k, "dk")
     dv = _grad_output(dv, v, "dv")
-    _call_bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_q=cu_seqlens_q, cu_k=cu_seqlens_k,
-              batch=cu_seqlens_q.numel() - 1, seqlen_q=max_seqlen_q, seqlen_k=max_seqlen_k,
-              heads_q=q.size(1), heads_k=k.size(1), is_causal=is_causal,
-              deterministic=deterministic)
+    ws = _call_bwd(dout, q, k, v, out, softmax_lse, dq, dk, dv, cu_q=cu_seqlens_q, cu_k=cu_seqlens_k,
+                   batch=cu_seqlens_q.numel() - 1, seqlen_q=max_seqlen_q, seqlen_k=max_seqlen_k,
+                   heads_q=q.size(1), heads_k=k.size(1), is_causal=is_causal,
+                   deterministic=deterministic)
+    _remember_workspace("backward_varlen", ws)
     return dq, dk, dv
 
 

@@ -28,37 +28,35 @@ MAX_WORLD_SIZE = 8
 _OPENED: dict = {}
 
 
+def _env_int(name: str) -> Optional[int]:
+    value = os.environ.get(name)
+    return None if value is None else int(value)
+
+
 def _resolve_parallel_context(local_rank: Optional[int], local_world_size: Optional[int]
                               ) -> Tuple[int, int]:
-    """Local rank / world size from arguments, environment or torch.distributed; rejects
-    multi-node jobs (reference: min_fa3_op.py:145-178)."""
-    if local_rank is None:
-        env_local_rank = os.environ.get("LOCAL_RANK")
-        if env_local_rank is not None:
-            local_rank = int(env_local_rank)
-        else:
-            if not torch.cuda.is_available():
-                raise RuntimeError("CUDA is required for parallel_remote_load")
-            local_rank = torch.cuda.current_device()
-    if local_world_size is None:
-        env_local_world_size = os.environ.get("LOCAL_WORLD_SIZE")
-        if env_local_world_size is not None:
-            local_world_size = int(env_local_world_size)
-        elif dist.is_available() and dist.is_initialized():
-            local_world_size = dist.get_world_size()
-        else:
-            raise RuntimeError(
-                "local_world_size is required when LOCAL_WORLD_SIZE is not set "
-                "and torch.distributed is not initialized"
-            )
-    if dist.is_available() and dist.is_initialized():
-        world_size = dist.get_world_size()
-        if world_size != local_world_size:
-            raise RuntimeError(
-                "ThunderKittens parallel IPC path is single-node only: "
-                f"world_size={world_size}, local_world_size={local_world_size}"
-            )
-    return int(local_rank), int(local_world_size)
+    """Fills in a missing local rank / local world size the way the reference does
+    (min_fa3_op.py:145-178): an explicit argument wins, then ``LOCAL_RANK`` / ``LOCAL_WORLD_SIZE``
+    from the launcher's environment, then the current CUDA device for the rank and the size of
+    the initialised process group for the world.  A process group that spans more ranks than
+    the local world size means several nodes, which peer mappings cannot cross: rejected with
+    the reference's message."""
+    group_size = dist.get_world_size() if dist.is_available() and dist.is_initialized() else None
+    rank = local_rank if local_rank is not None else _env_int("LOCAL_RANK")
+    if rank is None:
+        if not torch.cuda.is_available():
+            raise RuntimeError("CUDA is required for parallel_remote_load")
+        rank = torch.cuda.current_device()
+    world = local_world_size if local_world_size is not None else _env_int("LOCAL_WORLD_SIZE")
+    if world is None:
+        world = group_size
+    if world is None:
+        raise RuntimeError("local_world_size is required when LOCAL_WORLD_SIZE is not set "
+                           "and torch.distributed is not initialized")
+    if group_size is not None and group_size != world:
+        raise RuntimeError("ThunderKittens parallel IPC path is single-node only: "
+                           f"world_size={group_size}, local_world_size={world}")
+    return int(rank), int(world)
 
 
 class TKParallelTensor:

@@ -18,7 +18,8 @@ import torch
 
 from . import _cabi
 from .min_fa3_op import (_INT32_MAX, _call_fwd, _check, _check_cu_seqlens, _check_cu_seqlens_host,
-                         _check_device_capability, _check_varlen_qkv, _stream_ptr, _workspace)
+                         _check_device_capability, _check_varlen_qkv, _remember_workspace, _stream_ptr,
+                         _workspace)
 from .parallel import TKParallelTensor
 
 __all__ = ["forward_varlen_ring", "forward_varlen_mega_ring", "backward_varlen_mega_ring"]
@@ -89,9 +90,10 @@ def forward_varlen_ring(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_s
                         ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
     """Attention of ``q`` over the current ``k, v`` merged in place into the running
     ``out`` / ``lse`` (defaults: zeros / -inf), while ``num_comm_sm`` copy CTAs prefetch
-    ``src_rank``'s K/V from the parallel tensors into ``prefetch_k`` / ``prefetch_v``.
-    The copy runs on a side stream next to the attention kernel (limited to ``num_comp_sm``
-    CTAs) and is joined before the call returns control of the stream."""
+    ``src_rank``'s K/V from the parallel tensors into ``prefetch_k`` / ``prefetch_v`` -- all in
+    one launch on the current stream (``num_comp_sm`` attention CTAs followed by ``num_comm_sm``
+    copy CTAs, which join the attention work once their share of the copy is done).  With
+    ``num_comm_sm == 0`` nothing is copied (csrc/min_fa3_varlen_ring_bindings.cu:343-348)."""
     max_seqlen_q, max_seqlen_k = int(max_seqlen_q), int(max_seqlen_k)
     num_comp_sm, num_comm_sm, src_rank, ring_step = (int(num_comp_sm), int(num_comm_sm), int(src_rank),
                                                     int(ring_step))
@@ -142,30 +144,19 @@ def forward_varlen_ring(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_s
     else:
         _check_lse(lse, q, "lse")
 
-    main = torch.cuda.current_stream(q.device)
-    side = None
-    if num_comm_sm > 0:
+    # One launch, as in the reference (include/min_fa3_varlen_ring_launch.h:217): CTAs
+    # [0, num_comp_sm) run attention, CTAs [num_comp_sm, num_comp_sm + num_comm_sm) first pull
+    # src_rank's K/V through the peer mapping into the prefetch buffers.
+    prefetch = None
+    if num_comm_sm > 0 and k.numel() > 0:
         if prefetch_k is None:
             prefetch_k, prefetch_v = torch.empty_like(k), torch.empty_like(v)
-        lib = _cabi.load()
-        side = torch.cuda.Stream(device=q.device)
-        side.wait_stream(main)
-        nbytes = k.numel() * 2
-        with torch.cuda.device(q.device), torch.cuda.stream(side):
-            sp = ctypes.c_void_p(side.cuda_stream)
-            _cabi.check(lib.b2a_peer_copy(ctypes.c_void_p(prefetch_k.data_ptr()),
-                                          ctypes.c_void_p(remote_k.raw_ptrs_[src_rank]), nbytes,
-                                          max(1, num_comm_sm // 2 or 1), None, sp))
-            _cabi.check(lib.b2a_peer_copy(ctypes.c_void_p(prefetch_v.data_ptr()),
-                                          ctypes.c_void_p(remote_v.raw_ptrs_[src_rank]), nbytes,
-                                          max(1, num_comm_sm - num_comm_sm // 2), None, sp))
-        prefetch_k.record_stream(side)
-        prefetch_v.record_stream(side)
-    _call_fwd(q, k, v, out, lse, cu_q=cu_seqlens_q, cu_k=cu_seqlens_k, batch=batch,
-              seqlen_q=max_seqlen_q, seqlen_k=max_seqlen_k, heads_q=q.size(1), heads_k=k.size(1),
-              is_causal=is_causal, merge_running=True, grid_blocks=num_comp_sm)
-    if side is not None:
-        main.wait_stream(side)
+        prefetch = (remote_k.raw_ptrs_[src_rank], remote_v.raw_ptrs_[src_rank], prefetch_k, prefetch_v,
+                    num_comm_sm)
+    ws = _call_fwd(q, k, v, out, lse, cu_q=cu_seqlens_q, cu_k=cu_seqlens_k, batch=batch,
+                   seqlen_q=max_seqlen_q, seqlen_k=max_seqlen_k, heads_q=q.size(1), heads_k=k.size(1),
+                   is_causal=is_causal, merge_running=True, grid_blocks=num_comp_sm, prefetch=prefetch)
+    _remember_workspace("forward_varlen_ring", ws)
     if return_lse:
         return out, lse
     return out
@@ -312,7 +303,7 @@ def forward_varlen_mega_ring(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, 
     a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
     with torch.cuda.device(q.device):
         _cabi.check(lib.b2a_ring_fwd(ctypes.byref(a), _stream_ptr(q.device)))
-    forward_varlen_mega_ring.last_workspace = ws
+    _remember_workspace("forward_varlen_mega_ring", ws)
     if return_lse:
         return out, lse
     return out
@@ -321,14 +312,154 @@ def forward_varlen_mega_ring(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, 
 # --------------------------------------------------------------------------------------
 # context-parallel backward
 # --------------------------------------------------------------------------------------
-def _check_parallel_identity(t: TKParallelTensor, q: torch.Tensor, world: int, rank: int, name: str) -> None:
+def dkv_accum_numel(heads_k: int, logical_rank_capacity: int, batch: int) -> int:
+    """Floats each of ``remote_dk_accum`` / ``remote_dv_accum`` must hold: the reference's rule
+    ``KVH * round128(logical_rank_capacity + B * 128) * 128``
+    (csrc/backward/min_fa3_bwd_bindings.cu:630-640), where ``logical_rank_capacity`` is the largest
+    number of key rows any rank holds and ``B`` the number of documents."""
+    padded = ((int(logical_rank_capacity) + int(batch) * 128 + 127) // 128) * 128
+    return int(heads_k) * padded * 128
+
+
+def _check_parallel_identity(t, q: torch.Tensor, world: int, rank: int, name: str, device_type: str) -> None:
     # reference: csrc/backward/min_fa3_bwd_bindings.cu:359-373
     _check(isinstance(t, TKParallelTensor), f"{name} must be a TKParallelTensor")
-    _check(t.data_.is_cuda, f"{name} must be CUDA-backed")
+    _check(t.data_.device.type == device_type, f"{name} must be CUDA-backed")
     _check(t.data_.device == q.device, f"{name} local view must be on q.device")
     _check(t.local_world_size_ == world, f"{name} world size mismatch")
     _check(t.local_rank_ == rank, f"{name} local rank mismatch")
     _check(len(t.raw_ptrs_) == world, f"{name} must expose one pointer per rank")
+
+
+def _check_bwd_dense(t: torch.Tensor, name: str, device_type: str) -> None:
+    # check_bf16_cuda, csrc/backward/min_fa3_bwd_bindings.cu:40-46
+    _check(t.device.type == device_type, f"{name} must be a CUDA tensor")
+    _check(t.dtype == torch.bfloat16, f"{name} must have dtype torch.bfloat16")
+    _check(t.dim() == 3, f"{name} must have 3 dimensions")
+    _check(t.size(-1) == 128, f"{name} must have head_dim D=128")
+    _check(t.is_contiguous(), f"{name} must be contiguous")
+
+
+def _validate_backward_mega_ring(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
+                                 max_seqlen_k, cu_seqlens_q_host, cu_seqlens_k_host, remote_k, remote_v,
+                                 remote_dk_accum, remote_dv_accum, remote_dkv_completion, num_comp_sm,
+                                 num_comm_sm, global_seqlens_host, ring_sizes_host, ring_starts_host,
+                                 is_causal: bool, device_type: str = "cuda") -> Tuple[int, int, int, int, int]:
+    """Every host-side check of the context-parallel backward, in the order and with the texts of
+    the reference binding (csrc/backward/min_fa3_bwd_bindings.cu:398-545, 622-640) and of the
+    substrings its negative test matches on
+    (scripts/test_mega_ring/mega_ring_test_min_fa3_varlen_backward_validation_multi_rank.py:48-224).
+    Nothing is launched or allocated here.  Returns ``(world, rank, rank_kv_capacity, batch,
+    local_total_k)``.  ``device_type`` exists for the CPU-only tests of this function."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (out, "out"), (dout, "dout")):
+        _check_bwd_dense(t, name, device_type)
+    _check(softmax_lse.device.type == device_type, "softmax_lse must be a CUDA tensor")
+    _check(softmax_lse.dtype == torch.float32, "softmax_lse must have dtype torch.float32")
+    _check(softmax_lse.is_contiguous(), "softmax_lse must be contiguous")
+    _check(softmax_lse.device == q.device, "softmax_lse must be on the same CUDA device as q")
+    for t, name in ((cu_seqlens_q, "cu_seqlens_q"), (cu_seqlens_k, "cu_seqlens_k")):
+        _check(t.device.type == device_type, f"{name} must be a CUDA tensor")
+        _check(t.dtype == torch.int32, f"{name} must have dtype torch.int32")
+        _check(t.dim() == 1 and t.numel() >= 2, f"{name} must have shape [B + 1]")
+        _check(t.is_contiguous(), f"{name} must be contiguous")
+        _check(t.device == q.device, f"{name} must be on the same CUDA device as q")
+    hosts = (cu_seqlens_q_host, cu_seqlens_k_host)
+    _check(all(isinstance(t, torch.Tensor) and t.device.type == "cpu" for t in hosts),
+           "host cu_seqlens tensors must be on CPU")
+    _check(all(t.dtype == torch.int32 for t in hosts), "host cu_seqlens tensors must have dtype int32")
+    _check(all(t.is_contiguous() for t in hosts), "host cu_seqlens tensors must be contiguous")
+    _check(cu_seqlens_q_host.numel() == cu_seqlens_q.numel() and cu_seqlens_k_host.numel() == cu_seqlens_k.numel(),
+           "host and device cu_seqlens lengths must match")
+    _check(cu_seqlens_q.numel() == cu_seqlens_k.numel(), "cu_seqlens_q and cu_seqlens_k must have the same B")
+    batch = cu_seqlens_q_host.numel() - 1
+    for t, name in ((global_seqlens_host, "global_seqlens_host"), (ring_sizes_host, "ring_sizes_host"),
+                    (ring_starts_host, "ring_starts_host")):
+        _check(isinstance(t, torch.Tensor) and t.device.type == "cpu", f"{name} must be a CPU tensor")
+        _check(t.dtype == torch.int32, f"{name} must have dtype int32")
+        _check(t.dim() == 1 and t.numel() == batch, f"{name} must have shape [B]")
+        _check(t.is_contiguous(), f"{name} must be contiguous")
+    _check(all(t.device == q.device for t in (k, v, out, dout)), "all dense tensors must be on the same CUDA device")
+    _check(out.shape == q.shape and dout.shape == q.shape, "out and dout must have the same shape as q")
+    _check(q.size(1) > 0 and k.size(1) > 0, "qhead and kvhead must be positive")
+    _check(q.size(1) % k.size(1) == 0, "qhead must be divisible by kvhead")
+    _check(k.size(1) == v.size(1) and k.size(2) == v.size(2), "k/v shapes must match")
+    _check(tuple(softmax_lse.shape) == (q.size(1), q.size(0)), "softmax_lse must have shape [QH, total_q]")
+    # The reference wants both counts positive; a single-rank world has nothing to copy, so
+    # num_comm_sm = 0 is accepted there.
+    _check(num_comp_sm > 0 and num_comm_sm >= 0,
+           "mega-ring backward requires positive compute and communication SM counts")
+    if q.is_cuda:
+        _check_device_capability(q.device, "min_fa3_demo_b200 backward")
+        sm_count = torch.cuda.get_device_properties(q.device).multi_processor_count
+        _check(num_comp_sm + num_comm_sm <= sm_count,
+               f"num_comp_sm + num_comm_sm must not exceed the device SM count ({sm_count})")
+    _check(isinstance(remote_k, TKParallelTensor), "remote_k must be a TKParallelTensor")
+    world, rank = remote_k.local_world_size_, remote_k.local_rank_
+    _check(world in (1, 2, 4, 8), "world_size must be one of 1, 2, 4, or 8")
+    for t, name in ((remote_k, "remote_k"), (remote_v, "remote_v"), (remote_dk_accum, "remote_dk_accum"),
+                    (remote_dv_accum, "remote_dv_accum"), (remote_dkv_completion, "remote_dkv_completion")):
+        _check_parallel_identity(t, q, world, rank, name, device_type)
+    _check(remote_k.data_.dtype == torch.bfloat16 and remote_v.data_.dtype == torch.bfloat16 and
+           remote_k.data_.shape == k.shape and remote_v.data_.shape == v.shape,
+           "remote_k/remote_v must match the concatenated bf16 k/v storage")
+    _check(remote_k.data_.data_ptr() == k.data_ptr() and remote_v.data_.data_ptr() == v.data_ptr(),
+           "k/v must be the local remote_k/remote_v IPC arena views")
+    _check(remote_dk_accum.data_.dtype == torch.float32 and remote_dv_accum.data_.dtype == torch.float32,
+           "remote dK/dV accumulators must have dtype float32")
+    _check(remote_dkv_completion.data_.dtype == torch.int32 and remote_dkv_completion.data_.numel() == 1,
+           "remote_dkv_completion must be a one-element int32 parallel tensor")
+
+    cq, ck = cu_seqlens_q_host.tolist(), cu_seqlens_k_host.tolist()
+    glens, sizes, starts = global_seqlens_host.tolist(), ring_sizes_host.tolist(), ring_starts_host.tolist()
+    _check(cq[0] == 0 and ck[0] == 0, "cu_seqlens must start at zero")
+    local_total_k = ck[batch]
+    _check(k.size(0) == v.size(0) and k.size(0) % world == 0,
+           "k/v arena rows must match and be divisible by world_size")
+    cap = k.size(0) // world
+    _check(0 < cap <= _INT32_MAX, "rank_kv_capacity must be positive and fit in int32")
+    _check(cap % 128 == 0, f"rank_kv_capacity must be 128-row aligned. Got {cap}")
+    _check(0 <= local_total_k <= cap,
+           f"local_total_k must fit in rank_kv_capacity. Got {local_total_k} vs {cap}")
+    _check(cq[batch] == q.size(0), "cu_seqlens_q_host[-1] must equal q.size(0)")
+    prev, max_q, max_k = 8, 0, 0
+    rank_rows = [0] * world
+    for b in range(batch):
+        q_len, k_len = cq[b + 1] - cq[b], ck[b + 1] - ck[b]
+        _check(q_len >= 0 and k_len >= 0, f"cu_seqlens must be nondecreasing at batch={b}")
+        _check(q_len == k_len, f"causal hybrid backward requires self-attention q_len == k_len at batch={b}")
+        _check(q_len % 128 == 0, f"every local q/k length must be 128-row aligned at batch={b}")
+        _check(glens[b] > 0, f"global_seqlens_host must be positive at batch={b}")
+        _check(sizes[b] in (1, 2, 4, 8), f"ring_sizes_host must contain only 1, 2, 4, or 8 at batch={b}")
+        _check(sizes[b] <= prev, f"batch must be ordered by non-increasing ring size at batch={b}")
+        prev = sizes[b]
+        _check(starts[b] >= 0 and starts[b] % sizes[b] == 0 and starts[b] + sizes[b] <= world,
+               f"invalid aligned ring range at batch={b}: start={starts[b]}, size={sizes[b]}, world_size={world}")
+        _check(glens[b] % sizes[b] == 0, f"global length must be divisible by ring size at batch={b}")
+        member_rows = glens[b] // sizes[b]
+        for owner in range(starts[b], starts[b] + sizes[b]):
+            rank_rows[owner] += member_rows
+            _check(rank_rows[owner] <= _INT32_MAX, "logical rank K/V capacity must fit in int32")
+        member = starts[b] <= rank < starts[b] + sizes[b]
+        expected = member_rows if member else 0
+        _check(q_len == expected,
+               f"local q/k length does not match ring metadata at batch={b}. expected={expected}, actual={q_len}")
+        if is_causal and sizes[b] > 1 and member:
+            _check(q_len % 2 == 0 and (q_len // 2) % 128 == 0,
+                   f"G2/G4/G8 local half length must be 128-row aligned at batch={b}")
+        max_q, max_k = max(max_q, q_len), max(max_k, k_len)
+    _check(0 < max_seqlen_q <= _INT32_MAX and 0 < max_seqlen_k <= _INT32_MAX,
+           "max seqlens must be positive int32 values")
+    _check(max_q <= max_seqlen_q and max_k <= max_seqlen_k,
+           "max_seqlen_q/max_seqlen_k must cover every local sequence")
+    logical_cap = max(rank_rows)
+    _check(0 < logical_cap <= cap,
+           f"logical rank K/V capacity must be positive and fit in the reusable arena. Got {logical_cap} "
+           f"vs arena capacity {cap}")
+    need = dkv_accum_numel(k.size(1), logical_cap, batch)
+    _check(remote_dk_accum.data_.numel() >= need and remote_dv_accum.data_.numel() >= need,
+           "remote dK/dV accumulators must each contain (have capacity for) at least "
+           f"KVH * padded_rank_capacity * 128 = {need} float elements")
+    return world, rank, cap, batch, local_total_k
 
 
 def backward_varlen_mega_ring(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
@@ -343,53 +474,17 @@ def backward_varlen_mega_ring(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_
     reference by default, the non-causal ring is accepted too).
 
     ``k`` / ``v`` are the K/V arenas (``remote_k.data_`` / ``remote_v.data_``).  The fp32
-    accumulators ``remote_dk_accum`` / ``remote_dv_accum`` (>= ``KVH * rank_kv_capacity * 128``
-    floats) and the int32 ``remote_dkv_completion`` counter must be zeroed, and all ranks
-    synchronised, before every call.  Returns ``dq [total_q, QH, 128]`` and compact
-    ``dk, dv [local_total_k, KVH, 128]``."""
-    from .min_fa3_op import _check_bf16_cuda, _check_same_device
+    accumulators ``remote_dk_accum`` / ``remote_dv_accum`` (at least ``dkv_accum_numel(KVH,
+    logical_rank_capacity, B)`` floats, the reference's sizing rule) and the one-element int32
+    ``remote_dkv_completion`` counter must be zeroed, and all ranks synchronised, before every
+    call.  Returns ``dq [total_q, QH, 128]`` and compact ``dk, dv [local_total_k, KVH, 128]``."""
     max_seqlen_q, max_seqlen_k = int(max_seqlen_q), int(max_seqlen_k)
     num_comp_sm, num_comm_sm = int(num_comp_sm), int(num_comm_sm)
-    for t, name in ((q, "q"), (k, "k"), (v, "v"), (out, "out"), (dout, "dout")):
-        _check_bf16_cuda(t, name, 3)
-    _check(softmax_lse.is_cuda and softmax_lse.dtype == torch.float32 and softmax_lse.is_contiguous(),
-           "softmax_lse must be a contiguous CUDA float32 tensor")
-    _check(tuple(softmax_lse.shape) == (q.size(1), q.size(0)), "softmax_lse must have shape [QH, total_q]")
-    for t, name in ((k, "k"), (v, "v"), (out, "out"), (dout, "dout"), (softmax_lse, "softmax_lse")):
-        _check_same_device(q, t, name)
-    _check(out.shape == q.shape, "out must have the same shape as q")
-    _check(dout.shape == q.shape, "dout must have the same shape as q")
-    _check(k.size(1) == v.size(1), "k and v must have the same KV head count")
-    _check(q.size(1) % k.size(1) == 0, "qhead must be divisible by kvhead")
-    _check_cu_seqlens(cu_seqlens_q, "cu_seqlens_q")
-    _check_cu_seqlens(cu_seqlens_k, "cu_seqlens_k")
-    _check_cu_seqlens_host(cu_seqlens_q_host, cu_seqlens_q, "cu_seqlens_q_host")
-    _check_cu_seqlens_host(cu_seqlens_k_host, cu_seqlens_k, "cu_seqlens_k_host")
-    _check(num_comp_sm > 0, f"num_comp_sm must be positive. Got {num_comp_sm}")
-    _check(num_comm_sm >= 0, f"num_comm_sm must be non-negative. Got {num_comm_sm}")
-    _check_parallel_base(remote_k, "remote_k")
-    _check_parallel_base(remote_v, "remote_v")
-    world, rank = _ring_arena_checks(q, k, v, remote_k, remote_v, "mega ring backward", (1, 2, 4, 8))
-    for t, name in ((remote_dk_accum, "remote_dk_accum"), (remote_dv_accum, "remote_dv_accum"),
-                    (remote_dkv_completion, "remote_dkv_completion")):
-        _check_parallel_identity(t, q, world, rank, name)
-    _check(remote_dk_accum.data_.dtype == torch.float32 and remote_dv_accum.data_.dtype == torch.float32,
-           "remote_dk_accum and remote_dv_accum must have dtype torch.float32")
-    _check(remote_dkv_completion.data_.dtype == torch.int32 and remote_dkv_completion.data_.numel() >= 1,
-           "remote_dkv_completion must be an int32 tensor with at least one element")
-    _check_device_capability(q.device, "min_fa3_demo_b200 backward")
-    sm_count = torch.cuda.get_device_properties(q.device).multi_processor_count
-    _check(num_comp_sm + num_comm_sm <= sm_count,
-           f"num_comp_sm + num_comm_sm must not exceed the device SM count ({sm_count}). "
-           f"Got {num_comp_sm + num_comm_sm}")
-    cap = _validate_ring_metadata(q, k, cu_seqlens_q_host, cu_seqlens_k_host, global_seqlens_host,
-                                  ring_sizes_host, ring_starts_host, world, rank, bool(is_causal),
-                                  max_seqlen_q, max_seqlen_k)
-    need = k.size(1) * cap * 128
-    _check(remote_dk_accum.data_.numel() >= need and remote_dv_accum.data_.numel() >= need,
-           f"remote_dk_accum / remote_dv_accum need at least KVH * rank_kv_capacity * 128 = {need} floats")
-    batch = cu_seqlens_q_host.size(0) - 1
-    local_total_k = int(cu_seqlens_k_host[batch])
+    world, rank, cap, batch, local_total_k = _validate_backward_mega_ring(
+        dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+        cu_seqlens_q_host, cu_seqlens_k_host, remote_k, remote_v, remote_dk_accum, remote_dv_accum,
+        remote_dkv_completion, num_comp_sm, num_comm_sm, global_seqlens_host, ring_sizes_host,
+        ring_starts_host, bool(is_causal))
 
     dq = torch.empty_like(q)
     dk = torch.empty((local_total_k, k.size(1), 128), dtype=torch.bfloat16, device=q.device)
@@ -419,5 +514,5 @@ def backward_varlen_mega_ring(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_
     a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
     with torch.cuda.device(q.device):
         _cabi.check(lib.b2a_ring_bwd(ctypes.byref(a), _stream_ptr(q.device)))
-    backward_varlen_mega_ring.last_workspace = ws
+    _remember_workspace("backward_varlen_mega_ring", ws)
     return dq, dk, dv

@@ -174,6 +174,22 @@ def main() -> None:
                         out_b=bf16_bits(out_b), lse_b=lse_b.numpy(), merged_out=run_out.numpy(),
                         merged_lse=run_lse.squeeze(-1).transpose(0, 1).contiguous().numpy())
 
+    # 8) the same merge with a running output that is exactly representable in bf16 (the CUDA
+    # epilogue keeps the running output in bf16 between steps, min_fa3_epilogue.h:404-506), so a
+    # kernel can be held to this fixture without an input-rounding allowance.
+    gen8 = torch.Generator().manual_seed(88)
+    out_a = randn_bf16(gen8, 16, 4, 128).float()
+    lse_a = torch.randn(4, 16, generator=gen8)
+    out_b = randn_bf16(gen8, 16, 4, 128)
+    lse_b = torch.randn(4, 16, generator=gen8)
+    lse_a[0, 0] = float("-inf")          # a row whose running state is still empty
+    out_a[0, 0] = 0.0
+    run_out, run_lse = ring_common.update_out_and_lse(None, None, out_a, lse_a)
+    run_out, run_lse = ring_common.update_out_and_lse(run_out, run_lse, out_b, lse_b)
+    np.savez_compressed(OUT_DIR / "merge_bf16.npz", out_a=bf16_bits(out_a), lse_a=lse_a.numpy(),
+                        out_b=bf16_bits(out_b), lse_b=lse_b.numpy(), merged_out=run_out.numpy(),
+                        merged_lse=run_lse.squeeze(-1).transpose(0, 1).contiguous().numpy())
+
     for path in sorted(OUT_DIR.glob("*.npz")):
         print(f"{path.name}: {path.stat().st_size} bytes")
 

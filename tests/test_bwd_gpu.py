@@ -212,3 +212,70 @@ def test_varlen_backward_deterministic_repeats_bitwise():
     assert torch.equal(runs[0][1], plain[1]) and torch.equal(runs[0][2], plain[2])
     scale = max(1.0, plain[0].float().abs().max().item())
     assert (runs[0][0].float() - plain[0].float()).abs().max().item() <= 2.0 ** -6 * scale
+
+
+# --------------------------------------------------------------------------------------
+# Benchmark configuration 3 at full size: 65,536 packed tokens, 34 log-normal documents of
+# 128 ... 7,731 tokens (not multiples of 128), QH=32, KVH=8.  O and LSE of sampled rows of
+# every document (all heads) and dQ / dK / dV of one KV-head group on a subset of documents
+# (longest, shortest and four in between) against the fp32 oracle under the acceptance rule.
+# --------------------------------------------------------------------------------------
+def test_config3_full_size_against_oracle():
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+    from bench import varlen_lengths
+
+    lens = varlen_lengths()
+    assert sum(lens) == 65536 and min(lens) >= 1
+    qh, kvh, group = 32, 8, 4
+    total = sum(lens)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn(total, qh, 128, device="cuda", generator=gen).to(torch.bfloat16)
+    k = torch.randn(total, kvh, 128, device="cuda", generator=gen).to(torch.bfloat16)
+    v = torch.randn(total, kvh, 128, device="cuda", generator=gen).to(torch.bfloat16)
+    dout = torch.randn(total, qh, 128, device="cuda", generator=gen).to(torch.bfloat16)
+    cu = torch.tensor([0, *torch.tensor(lens).cumsum(0).tolist()], dtype=torch.int32)
+    cud = cu.cuda()
+    mx = max(lens)
+    out, lse = min_fa3_op.forward_varlen(q, k, v, cud, cud, mx, mx, True, cu_seqlens_q_host=cu,
+                                         cu_seqlens_k_host=cu, return_lse=True)
+    dq, dk, dv = min_fa3_op.backward_varlen(dout, q, k, v, out, lse, cud, cud, mx, mx, True)
+    torch.cuda.synchronize()
+    min_fa3_op.check_last_status()
+    assert all(torch.isfinite(t.float()).all() for t in (out, lse, dq, dk, dv))
+
+    # forward: up to 12 sampled rows per document, all heads
+    for i, n in enumerate(lens):
+        s0 = int(cu[i])
+        rows = sorted({0, n - 1, n // 2, min(n - 1, 127), min(n - 1, 128), max(0, n - 129),
+                       *[(7919 * (j + 1) * (i + 1)) % n for j in range(6)]})
+        rows_t = torch.tensor(rows)
+        qs = q[s0 + rows_t].cpu()
+        ks, vs = k[s0:s0 + n].cpu(), v[s0:s0 + n].cpu()
+        ref_o, ref_l = orc.attention_positions(qs, ks, vs, rows_t, torch.arange(n))
+        # bf16 yardstick on the same rows: bf16 scores / probabilities / output
+        sc = torch.einsum("qhd,khd->hqk", qs, ks.repeat_interleave(group, dim=1)).float() * (128 ** -0.5)
+        sc = sc.masked_fill(torch.arange(n)[None, None, :] > rows_t[None, :, None], float("-inf"))
+        pb = torch.softmax(sc, dim=-1).to(torch.bfloat16)
+        ob = torch.einsum("hqk,khd->qhd", pb, vs.repeat_interleave(group, dim=1))
+        e = (ob.float() - ref_o).abs().max().item()
+        err = (out[s0 + rows_t].float().cpu() - ref_o).abs().max().item()
+        assert err <= bound(e), f"doc {i} (len {n}): O error {err:.3e} exceeds {bound(e):.3e}"
+        lerr = (lse[:, s0 + rows_t].cpu() - ref_l).abs().max().item()
+        assert lerr <= 1e-3, f"doc {i} (len {n}): LSE error {lerr:.3e}"
+
+    # backward: one KV-head group (query heads 28..31, KV head 7), whole documents
+    order = sorted(range(len(lens)), key=lambda i: lens[i])
+    chosen = {order[-1], order[0], order[len(order) // 4], order[len(order) // 2], order[(3 * len(order)) // 4],
+              order[-3]}
+    for i in sorted(chosen):
+        s0, n = int(cu[i]), lens[i]
+        qs, ds = q[s0:s0 + n, 28:32].cpu()[None], dout[s0:s0 + n, 28:32].cpu()[None]
+        ks, vs = k[s0:s0 + n, 7:8].cpu()[None], v[s0:s0 + n, 7:8].cpu()[None]
+        rq, rk, rv = orc.bshd_backward(qs, ks, vs, ds, True)
+        e = orc.bf16_attention_error(qs, ks, vs, True, ds)
+        assert_within(f"dQ doc {i} (len {n})", dq[s0:s0 + n, 28:32][None], rq, e["dq"])
+        # dK / dV of KV head 7 only receive contributions from query heads 28..31
+        assert_within(f"dK doc {i} (len {n})", dk[s0:s0 + n, 7:8][None], rk, e["dk"])
+        assert_within(f"dV doc {i} (len {n})", dv[s0:s0 + n, 7:8][None], rv, e["dv"])

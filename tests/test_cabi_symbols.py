@@ -44,10 +44,29 @@ def test_abi_version_and_error_text(lib):
     assert isinstance(_cabi.last_error(), str)
 
 
-def test_struct_sizes_match_c_layout():
-    # pointers (8) first, then int32 fields, float, pointer, size_t: no surprises in padding
-    assert ctypes.sizeof(_cabi.FwdArgs) == 7 * 8 + 11 * 4 + 4 + 8 + 8
-    assert ctypes.sizeof(_cabi.BwdArgs) == 11 * 8 + 11 * 4 + 4 + 8 + 8
+def test_struct_sizes_match_c_layout(tmp_path):
+    # The header is plain C: compile it with the C compiler and compare every struct's size and
+    # the offset of its last field with the ctypes mirror.
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc") or shutil.which("cc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    structs = {"b2a_fwd_args": (_cabi.FwdArgs, "prefetch_blocks"), "b2a_bwd_args": (_cabi.BwdArgs, "workspace_bytes"),
+               "b2a_ring_fwd_args": (_cabi.RingFwdArgs, "workspace_bytes"),
+               "b2a_ring_bwd_args": (_cabi.RingBwdArgs, "workspace_bytes")}
+    lines = "".join(f'printf("{name} %zu %zu\\n", sizeof({name}), offsetof({name}, {last}));\n'
+                    for name, (_, last) in structs.items())
+    src = tmp_path / "sizes.c"
+    src.write_text(f'#include <stdio.h>\n#include <stddef.h>\n#include "{HEADER}"\nint main(void) {{\n{lines}return 0;\n}}\n')
+    exe = tmp_path / "sizes"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    for line in filter(None, out):
+        name, size, off = line.split()
+        mirror, last = structs[name]
+        assert ctypes.sizeof(mirror) == int(size), name
+        assert getattr(mirror, last).offset == int(off), name
 
 
 def test_argument_validation_without_gpu(lib):

@@ -81,6 +81,15 @@ def test_noalloc_forward_matches_regular_entry_point_twice_in_a_row():
         out, lse = torch.full_like(qv, 7.0), torch.full((4, 1019), 7.0, device="cuda")
         _run_noalloc(lib, _args(qv, kv, vv, out, lse, True, cu, max(lengths)))
         assert torch.equal(out, ref_out) and torch.equal(lse, ref_lse)
+        # the status word of the built-in scratch is read by passing no workspace
+        assert lib.b2a_check_status(None, None) == _cabi.B2A_OK, _cabi.last_error()
+
+    # and the result is right on its own account, not only equal to the other entry point
+    from oracle import attention_oracle as orc
+    cu_list = cu.cpu().tolist()
+    want_out, want_lse = orc.varlen_forward(qv.cpu(), kv.cpu(), vv.cpu(), cu_list, cu_list, True)
+    assert (out.float().cpu() - want_out).abs().max().item() <= 1.6e-2
+    assert (lse.cpu() - want_lse).abs().max().item() <= 1e-3
 
 
 def test_noalloc_rejects_problems_beyond_its_scratch():
