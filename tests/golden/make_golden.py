@@ -182,8 +182,6 @@ def main() -> None:
     lse_a = torch.randn(4, 16, generator=gen8)
     out_b = randn_bf16(gen8, 16, 4, 128)
     lse_b = torch.randn(4, 16, generator=gen8)
-    lse_a[0, 0] = float("-inf")          # a row whose running state is still empty
-    out_a[0, 0] = 0.0
     run_out, run_lse = ring_common.update_out_and_lse(None, None, out_a, lse_a)
     run_out, run_lse = ring_common.update_out_and_lse(run_out, run_lse, out_b, lse_b)
     np.savez_compressed(OUT_DIR / "merge_bf16.npz", out_a=bf16_bits(out_a), lse_a=lse_a.numpy(),

@@ -125,3 +125,38 @@ def test_causal_sequence_as_two_merged_ring_steps():
     err = (out.float().cpu() - ref_out[half:]).abs().max().item()
     assert err <= bound(e), f"O error {err:.3e} exceeds {bound(e):.3e}"
     assert (lse.cpu() - ref_lse[:, half:]).abs().max().item() <= LSE_ATOL
+
+
+@pytest.mark.parametrize("rows,blocks", [(333, 4), (1024, 3), (64, 8)])
+def test_ring_step_copies_and_computes_in_one_launch(rows, blocks):
+    """The ring step's copy CTAs (``prefetch_*`` fields of the forward arguments) ride in the
+    attention launch: the prefetch buffers end up bit-exact copies of the source buffers -- whole
+    32 KiB pieces plus a shorter tail -- and the attention result is the one of a launch without
+    copy CTAs.  The source stands in for another rank's K/V (here: other buffers of the same GPU)."""
+    qh, kvh = 4, 2
+    q, k, v, _dout, cu = make_varlen(21, [rows], qh, kvh)
+    gen = torch.Generator().manual_seed(22)
+    src_k = torch.randn(rows, kvh, 128, generator=gen).to(torch.bfloat16).to(DEV)
+    src_v = torch.randn(rows, kvh, 128, generator=gen).to(torch.bfloat16).to(DEV)
+    dst_k = torch.full_like(src_k, -7.0)
+    dst_v = torch.full_like(src_v, -7.0)
+    qd, kd, vd, cud = q.to(DEV), k.to(DEV), v.to(DEV), cu.to(DEV)
+
+    def call(prefetch):
+        out = torch.zeros_like(qd)
+        lse = torch.full((qh, rows), float("-inf"), dtype=torch.float32, device=DEV)
+        ws = _call_fwd(qd, kd, vd, out, lse, cu_q=cud, cu_k=cud, batch=1, seqlen_q=rows, seqlen_k=rows,
+                       heads_q=qh, heads_k=kvh, is_causal=True, merge_running=True, grid_blocks=16,
+                       prefetch=prefetch)
+        torch.cuda.synchronize()
+        check_device_status(ws)
+        return out, lse
+
+    plain_out, plain_lse = call(None)
+    out, lse = call((src_k.data_ptr(), src_v.data_ptr(), dst_k, dst_v, blocks))
+    assert torch.equal(dst_k, src_k) and torch.equal(dst_v, src_v)
+    assert torch.equal(out, plain_out) and torch.equal(lse, plain_lse)
+    ref_out, ref_lse = orc.varlen_forward(q, k, v, [0, rows], [0, rows], True)
+    e = orc.bf16_attention_error(q[None], k[None], v[None], True)["o"]
+    assert (out.float().cpu() - ref_out).abs().max().item() <= bound(e)
+    assert (lse.cpu() - ref_lse).abs().max().item() <= LSE_ATOL
