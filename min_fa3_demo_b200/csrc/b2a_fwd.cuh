@@ -87,6 +87,7 @@ struct FwdParams {
     uint8_t* arena_k;                  // this rank's arena (the tensor maps of K/V cover it)
     uint8_t* arena_v;
     int* kv_flags;                     // per 128-row arena block: 1 once K and V have landed
+    int* copy_done;                    // number of copy CTAs that have finished all their tasks
     // ---- ring step mode: CTAs [num_comp, gridDim.x) first copy two flat buffers (another rank's
     // K and V) into local prefetch buffers, then join the attention work queue.  0 otherwise.
     const uint8_t* prefetch_src[2];
@@ -336,6 +337,10 @@ __device__ __forceinline__ void ring_copy_role(const FwdParams& p, FwdShared& sh
             }
         }
         bulk_wait_group<0>();
+        // Once every copy CTA has reported here, all remote blocks are in place and the load
+        // warps stop looking at per-block flags.
+        fence_proxy_async_all();
+        asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p.copy_done), "r"(ok ? 1 : 0) : "memory");
     }
 }
 
@@ -451,6 +456,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             uint32_t kv_it = 0;
             uint32_t q_cnt[2] = {0, 0};
             bool ok = true;
+            // Ring mode: true once all copy CTAs are done, i.e. every remote block has landed.
+            bool all_landed = p.ring_docs == nullptr || p.comm_task_count == 0;
+            const int copy_ctas = static_cast<int>(gridDim.x) - p.num_comp;
             for (uint32_t it = 0; ok; ++it) {
                 const uint32_t slot = it & 1u;
                 ok = mbar_wait(wctx, smem_u32(&sh.sched_empty[slot]), ((it >> 1) & 1u) ^ 1u, 1);
@@ -497,9 +505,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                         if (p.ring_docs != nullptr) {
                             bool remote = false;
                             row = ring_kv_row(p, wk, j, &remote);
-                            if (remote && kv == 0) {
-                                ok = flag_wait(wctx, p.kv_flags + row / kTileN, 13);
-                                if (!ok) break;
+                            if (remote && kv == 0 && !all_landed) {
+                                int landed;
+                                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(landed) : "l"(p.copy_done)
+                                             : "memory");
+                                if (landed >= copy_ctas) {
+                                    all_landed = true;
+                                } else {
+                                    ok = flag_wait(wctx, p.kv_flags + row / kTileN, 13);
+                                    if (!ok) break;
+                                }
                                 fence_proxy_async_all();
                             }
                         }

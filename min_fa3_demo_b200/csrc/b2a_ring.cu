@@ -172,6 +172,7 @@ int b2a_ring_fwd(const b2a_ring_fwd_args* a, void* cuda_stream) {
     p.arena_k = static_cast<uint8_t*>(a->arena_k);
     p.arena_v = static_cast<uint8_t*>(a->arena_v);
     p.kv_flags = reinterpret_cast<int*>(ws + lay.flags_off);
+    p.copy_done = &hdr->reserved;
 
     const int comm = p.comm_task_count > 0 ? a->num_comm_sm : 0;
     int grid = a->num_comp_sm + comm;
