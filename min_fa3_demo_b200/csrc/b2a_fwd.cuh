@@ -549,28 +549,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 
             // S_x = Q_x * K^T for the K tile in `stage` (8 k-steps of 16 over head_dim).
             auto issue_qk = [&](int x, uint32_t stage) {
-                const uint32_t b0 = k_lo0 + stage * kStageStep;
-#pragma unroll
-                for (int ks = 0; ks < kHeadDim / 16; ++ks) {
-                    umma_ss_lo_w(s_tmem[x], q_lo[x] + kstep_kmajor(ks), b0 + kstep_kmajor(ks), idesc_qk,
-                               ks > 0 ? 1u : 0u);
-                }
+                umma_ss_kk_x8_w(s_tmem[x], q_lo[x], k_lo0 + stage * kStageStep, idesc_qk, 0u);
             };
             // O_x (+)= P_x * V for the V tile in `stage` (8 k-steps of 16 over keys).
             auto issue_pv = [&](int x, uint32_t stage, uint32_t accumulate) {
-                const uint32_t b0 = v_lo0 + stage * kStageStep;
-#pragma unroll
-                for (int ks = 0; ks < kTileN / 16; ++ks) {
-                    umma_ts_lo_w(o_tmem[x], s_tmem[x] + ks * 8, b0 + kstep_mnmajor(ks), idesc_pv,
-                               (ks > 0 || accumulate) ? 1u : 0u);
-                }
+                umma_ts_x8_w(o_tmem[x], s_tmem[x], v_lo0 + stage * kStageStep, idesc_pv, accumulate);
             };
 
             for (uint32_t it = 0; ok; ++it) {
                 const uint32_t slot = it & 1u;
                 ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 4);
                 if (!ok) break;
-                const int w = *reinterpret_cast<volatile int*>(&sh.sched_w[slot]);
+                // Broadcast from lane 0 so that everything derived from the work index (block counts,
+                // ring stages, operand descriptors) is provably warp-uniform for the compiler.
+                const int w = __shfl_sync(0xFFFFFFFFu, *reinterpret_cast<volatile int*>(&sh.sched_w[slot]), 0);
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(smem_u32(&sh.sched_empty[slot]));

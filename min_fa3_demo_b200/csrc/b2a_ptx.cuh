@@ -410,6 +410,248 @@ __device__ __forceinline__ void umma_ts_lo_w(uint32_t d_tmem, uint32_t a_tmem, u
         : "memory");
 }
 
+// Whole-contraction forms: the eight (or four) k-steps of one 128 x N x 128 (or x 64) product as
+// ONE instruction group with a single lane election, so that the issuing warp spends a handful
+// of instructions per MMA instead of an election, a predicate and two register pairs each.
+// `accumulate` applies to the first k-step; the others always accumulate.
+// A and B both K-major [rows][128] tiles.
+__device__ __forceinline__ void umma_ss_kk_x8_w(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pe, pt;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 ra, rb;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "elect.sync _|pe, 0xFFFFFFFF;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t"
+        "add.u32 ra, %1, 2;\n\t"
+        "add.u32 rb, %2, 2;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 4;\n\t"
+        "add.u32 rb, %2, 4;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 6;\n\t"
+        "add.u32 rb, %2, 6;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 1024;\n\t"
+        "add.u32 rb, %2, 1024;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 1026;\n\t"
+        "add.u32 rb, %2, 1026;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 1028;\n\t"
+        "add.u32 rb, %2, 1028;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 1030;\n\t"
+        "add.u32 rb, %2, 1030;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
+// A and B both MN-major tiles.
+__device__ __forceinline__ void umma_ss_nn_x8_w(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pe, pt;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 ra, rb;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "elect.sync _|pe, 0xFFFFFFFF;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t"
+        "add.u32 ra, %1, 128;\n\t"
+        "add.u32 rb, %2, 128;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 256;\n\t"
+        "add.u32 rb, %2, 256;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 384;\n\t"
+        "add.u32 rb, %2, 384;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 512;\n\t"
+        "add.u32 rb, %2, 512;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 640;\n\t"
+        "add.u32 rb, %2, 640;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 768;\n\t"
+        "add.u32 rb, %2, 768;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 896;\n\t"
+        "add.u32 rb, %2, 896;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
+// A K-major, B MN-major.
+__device__ __forceinline__ void umma_ss_kn_x8_w(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pe, pt;\n\t"
+        ".reg .b64 da, db;\n\t"
+        ".reg .b32 ra, rb;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "elect.sync _|pe, 0xFFFFFFFF;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t"
+        "add.u32 ra, %1, 2;\n\t"
+        "add.u32 rb, %2, 128;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 4;\n\t"
+        "add.u32 rb, %2, 256;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 6;\n\t"
+        "add.u32 rb, %2, 384;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 1024;\n\t"
+        "add.u32 rb, %2, 512;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 1026;\n\t"
+        "add.u32 rb, %2, 640;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 1028;\n\t"
+        "add.u32 rb, %2, 768;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "add.u32 ra, %1, 1030;\n\t"
+        "add.u32 rb, %2, 896;\n\t"
+        "mov.b64 da, {ra, %5};\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pt;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
+// A from tensor memory (8 columns per k-step), B MN-major.
+__device__ __forceinline__ void umma_ts_x8_w(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pe, pt;\n\t"
+        ".reg .b64 db;\n\t"
+        ".reg .b32 ra, rb;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "elect.sync _|pe, 0xFFFFFFFF;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t"
+        "add.u32 ra, %1, 8;\n\t"
+        "add.u32 rb, %2, 128;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "add.u32 ra, %1, 16;\n\t"
+        "add.u32 rb, %2, 256;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "add.u32 ra, %1, 24;\n\t"
+        "add.u32 rb, %2, 384;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "add.u32 ra, %1, 32;\n\t"
+        "add.u32 rb, %2, 512;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "add.u32 ra, %1, 40;\n\t"
+        "add.u32 rb, %2, 640;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "add.u32 ra, %1, 48;\n\t"
+        "add.u32 rb, %2, 768;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "add.u32 ra, %1, 56;\n\t"
+        "add.u32 rb, %2, 896;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
+// Four k-steps (64 contraction elements): A from tensor memory, B MN-major.
+__device__ __forceinline__ void umma_ts_x4_w(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pe, pt;\n\t"
+        ".reg .b64 db;\n\t"
+        ".reg .b32 ra, rb;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "elect.sync _|pe, 0xFFFFFFFF;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t"
+        "add.u32 ra, %1, 8;\n\t"
+        "add.u32 rb, %2, 128;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "add.u32 ra, %1, 16;\n\t"
+        "add.u32 rb, %2, 256;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "add.u32 ra, %1, 24;\n\t"
+        "add.u32 rb, %2, 384;\n\t"
+        "mov.b64 db, {rb, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, pt;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+
 // Same elected lane as the *_w MMA forms (the commit must come from the thread that issued them).
 __device__ __forceinline__ void tc_commit_w(uint32_t bar) {
     asm volatile(
