@@ -538,11 +538,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 
             // D[128 x 128] = A * B^T with both operands K-major [rows][128] tiles.
             auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    umma_ss_lo_w(d_tmem, a_lo + kstep_kmajor(ks), b_lo + kstep_kmajor(ks), idesc_kk,
-                               ks > 0 ? 1u : 0u);
-                }
+                umma_ss_kk_x8_w(d_tmem, a_lo, b_lo, idesc_kk, 0u);
             };
 
             uint32_t item_cnt = 0;
@@ -554,7 +550,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 const uint32_t slot = it & 1u;
                 ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 5);
                 if (!ok) break;
-                const int w = *reinterpret_cast<volatile int*>(&sh.sched_w[slot]);
+                const int w = __shfl_sync(0xFFFFFFFFu, *reinterpret_cast<volatile int*>(&sh.sched_w[slot]), 0);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&sh.sched_empty[slot]));
                 if (w < 0) break;
@@ -614,12 +610,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     }
                     tc_fence_after_sync();
                     {
-#pragma unroll
-                        for (int ks = 0; ks < 8; ++ks) {
-                            const uint32_t a_col = kColS + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
-                            umma_ts_lo_w(tmem_base + kColDV, tmem_base + a_col, do_lo_n + kstep_mnmajor(ks),
-                                       idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
-                        }
+                        // P^T sits in two runs of 32 packed columns (one per compute warpgroup).
+                        umma_ts_x4_w(tmem_base + kColDV, tmem_base + kColS, do_lo_n, idesc_kn, t > 0 ? 1u : 0u);
+                        umma_ts_x4_w(tmem_base + kColDV, tmem_base + kColS + 64, do_lo_n + kstep_mnmajor(4), idesc_kn, 1u);
                         tc_commit_w(smem_u32(&sh.do_empty[do_stage]));
                     }
                     __syncwarp();
@@ -648,17 +641,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     PH_MARK(3);
                     tc_fence_after_sync();
                     {
-#pragma unroll
-                        for (int ks = 0; ks < 8; ++ks) {
-                            umma_ss_lo_w(tmem_base + kColDP, ds_lo_n + kstep_mnmajor(ks), k_lo_n + kstep_mnmajor(ks),
-                                       idesc_nn, ks > 0 ? 1u : 0u);
-                        }
+                        umma_ss_nn_x8_w(tmem_base + kColDP, ds_lo_n, k_lo_n, idesc_nn, 0u);
                         tc_commit_w(smem_u32(&sh.dq_full));
-#pragma unroll
-                        for (int ks = 0; ks < 8; ++ks) {
-                            umma_ss_lo_w(tmem_base + kColDK, ds_lo_k + kstep_kmajor(ks), q_lo_n + kstep_mnmajor(ks),
-                                       idesc_kn, (t > 0 || ks > 0) ? 1u : 0u);
-                        }
+                        umma_ss_kn_x8_w(tmem_base + kColDK, ds_lo_k, q_lo_n, idesc_kn, t > 0 ? 1u : 0u);
                         tc_commit_w(smem_u32(&sh.q_empty[stage]));
                         tc_commit_w(smem_u32(&sh.ds_empty));
                         if (!has_next) {
