@@ -149,9 +149,6 @@ int b2a_bwd(const b2a_bwd_args* a, void* cuda_stream) {
     const int causal = a->is_causal ? 1 : 0;
 
     B2A_CUDA_OK(cudaMemsetAsync(hdr, 0, sizeof(WorkspaceHeader), stream));
-    B2A_CUDA_OK(cudaMemsetAsync(dq_accum, 0,
-                                static_cast<size_t>(a->heads_q) * lay.padded_q * kHeadDim * sizeof(float),
-                                stream));
     int* dq_sem = nullptr;
     if (a->deterministic) {
         dq_sem = reinterpret_cast<int*>(ws + lay.dq_sem_off);
@@ -166,6 +163,7 @@ int b2a_bwd(const b2a_bwd_args* a, void* cuda_stream) {
     pre.lse = a->lse;
     pre.lse2 = lse2;
     pre.dpsum = dpsum;
+    pre.dq_accum = dq_accum;     // cleared by the preprocess: no separate memset pass
     pre.cu_seqlens_q = a->cu_seqlens_q;
     pre.batch = a->batch;
     pre.seqlen_q = a->seqlen_q;
@@ -379,8 +377,6 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
 
     const float scale = 1.0f / std::sqrt(static_cast<float>(kHeadDim));
     if (a->total_q > 0) {
-        B2A_CUDA_OK(cudaMemsetAsync(dq_accum, 0, static_cast<size_t>(a->heads_q) * a->total_q * kHeadDim * sizeof(float),
-                                    stream));
         std::vector<uint8_t> host(lay.flags_off - lay.docs_off, 0);
         memcpy(host.data(), plan.docs.data(), plan.docs.size() * sizeof(RingDoc));
         int4* w = reinterpret_cast<int4*>(host.data() + (lay.work_off - lay.docs_off));
@@ -399,6 +395,7 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
         pre.lse = a->lse;
         pre.lse2 = lse2;
         pre.dpsum = dpsum;
+        pre.dq_accum = dq_accum;
         pre.batch = 1;
         pre.seqlen_q = a->total_q;
         pre.heads_q = a->heads_q;

@@ -18,7 +18,9 @@
 //   warp  8-11  dQ warpgroup: drains dQ tiles from tensor memory, red.add into dq_accum
 //   warp 12     tcgen05.mma issue
 //   warp 13     TMA loads and work fetch
-//   warp 14-15  idle
+//   warp 14     deterministic mode only: "scout" that watches the per-tile order counters ahead of
+//               the dQ warpgroup (otherwise idle)
+//   warp 15     idle
 //
 // Tensor memory (512 columns): S^T/P^T [0,128)  dP^T/dQ [128,256)  dV [256,384)  dK [384,512).
 #pragma once
@@ -52,8 +54,9 @@ struct BwdParams {
     float* dq_accum;               // see layout above
     int* dq_sem;                   // deterministic mode: per (query head, query tile) count of key blocks
                                    // already added, zeroed before launch; null otherwise
-    const float* lse2;             // [heads_q, padded_q]  (LSE * log2 e; +inf = row contributes nothing)
-    const float* dpsum;            // [heads_q, padded_q]  rowsum(dO * O)
+    const float* lse2;             // [heads_q, padded_q]  -(LSE * log2 e); -inf = row contributes nothing
+    const float* dpsum;            // [heads_q, padded_q]  -rowsum(dO * O)
+                                   // (both negated by the preprocess so that the main loop adds them)
     const int* cu_seqlens_q;
     const int* cu_seqlens_k;
     const int2* work_list;         // varlen: (doc, n_block) in LPT order
@@ -285,6 +288,7 @@ struct __align__(1024) BwdShared {
     int sched_w[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
+    uint32_t order_step;     // deterministic mode: dQ tiles (CTA-wide running count) cleared for adding
 };
 static_assert(sizeof(BwdShared) <= 232448, "backward shared storage exceeds the 227 KiB opt-in limit");
 
@@ -406,13 +410,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         mbar_init(smem_u32(&sh.dkv_empty), 256);
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&sh.sched_full[i]), 1);
-            mbar_init(smem_u32(&sh.sched_empty[i]), 1 + 12);   // MMA warp + 12 consumer warps
+            mbar_init(smem_u32(&sh.sched_empty[i]), 2 + 12);   // MMA warp, scout warp + 12 consumer warps
         }
         for (int i = 0; i < 6; ++i) {
             mbar_init(smem_u32(&sh.comm_full[i]), 1);
             mbar_init(smem_u32(&sh.comm_empty[i]), 1);
         }
         sh.abort_flag = 0;
+        sh.order_step = 0;
         fence_mbar_init();
         fence_proxy_async_smem();
     }
@@ -672,6 +677,46 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 }
             }
             PH_PRINT("mma", 7);
+        } else if (warp == 14) {
+            // ------------------------------------------------------------ order scout (deterministic mode)
+            // Additions into a dQ tile happen in ascending key-block order.  This warp walks the CTA's
+            // tile sequence ahead of the dQ warpgroup, waits (in global memory, with L2 latency) until
+            // a tile's counter says that the blocks below this one have been added, and then raises a
+            // step count in shared memory, which is all the dQ warpgroup looks at.
+            bool ok = true;
+            uint32_t cleared = 0;
+            const int pad_tiles = p.padded_q / kTileM;
+            for (uint32_t it = 0; ok; ++it) {
+                const uint32_t slot = it & 1u;
+                ok = mbar_wait(wctx, smem_u32(&sh.sched_full[slot]), (it >> 1) & 1u, 32);
+                if (!ok) break;
+                const int w = __shfl_sync(0xFFFFFFFFu, *reinterpret_cast<volatile int*>(&sh.sched_w[slot]), 0);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sh.sched_empty[slot]));
+                if (w < 0) break;
+                if (p.dq_sem == nullptr) continue;
+                const BwdWork wk = bwd_decode_work(p, w);
+                const int per_head = wk.count0 + wk.count1;
+                const int steps = per_head * group;
+                const int blk_index = wk.n0 / kTileN;
+                if (lane == 0) {
+                    for (int t = 0; t < steps && ok; ++t) {
+                        const int hq = wk.head_k * group + t / per_head;
+                        bool diag;
+                        const int q_local = bwd_step_row(wk, t % per_head, &diag);
+                        const int* sem = p.dq_sem + static_cast<long long>(hq) * pad_tiles +
+                                         (wk.q_pad_begin + q_local) / kTileM;
+                        // Work items are handed out in ascending block order per (document, head), so
+                        // the blocks waited for are running already; the wait is bounded all the same.
+                        ok = value_wait(wctx, sem, blk_index, 26);
+                        if (!ok) break;
+                        ++cleared;
+                        asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(&sh.order_step)), "r"(cleared)
+                                     : "memory");
+                    }
+                }
+                ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+            }
         }
     } else if (warp >= 8) {
         // -------------------------------------------------------------------- dQ warpgroup
@@ -680,8 +725,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t dq_tmem = tmem_base + lane_base + kColDP;
         uint32_t dq_cnt = 0;
-        int* prev_sem = nullptr;   // deterministic mode, thread 256: tile whose counter is still to be published
-        int prev_val = 0;
+        // Deterministic mode, thread 256: the two most recent tiles whose counters are still to be
+        // published (oldest first).  A tile is published once its four reductions have been performed.
+        int* pend_sem[2] = {nullptr, nullptr};
+        int pend_val[2] = {0, 0};
+        uint32_t tiles_seen = 0;   // dQ tiles of this CTA so far (matches the scout's count)
         bool ok = true;
         PH_DECL(4)   // 0 other, 1 wait dq_full, 2 load + arrive, 3 reductions
         for (uint32_t it = 0; ok; ++it) {
@@ -718,17 +766,35 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&sh.dq_drained));
                 PH_MARK(2);
-                // Deterministic mode: the key blocks of a document add into a dQ tile in ascending
-                // order.  Block n waits until the tile's counter says n blocks have been added.
-                // Work items are handed out in ascending block order per (document, head), so the
-                // blocks waited for are always running already; the wait is bounded all the same.
+                // Deterministic mode: the scout warp has checked that the key blocks below this one have
+                // been added to the tile; wait for its step count (shared memory, a few clocks when it
+                // is ahead, and bounded).
                 int* sem = nullptr;
                 const int blk_index = wk.n0 / kTileN;
                 if (p.dq_sem != nullptr) {
                     sem = p.dq_sem + static_cast<long long>(hq) * pad_tiles + (wk.q_pad_begin + q_local) / kTileM;
-                    // A wait that runs out raises the CTA's abort flag and status word; the warpgroup
-                    // still goes through this step's barriers together and stops at its next wait.
-                    if (threadIdx.x == 256) (void)value_wait(wctx, sem, blk_index, 26);
+                    ++tiles_seen;
+                    if (threadIdx.x == 256) {
+                        const uint32_t start = global_timer_lo();
+                        uint32_t polls = 0;
+                        while (true) {
+                            uint32_t cleared;
+                            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(cleared)
+                                         : "r"(smem_u32(&sh.order_step)) : "memory");
+                            if (cleared >= tiles_seen) break;
+                            if ((++polls & 0x3Fu) == 0u) {
+                                // A wait that runs out raises the CTA's abort flag and status word; the
+                                // warpgroup still goes through this step's barriers together and stops
+                                // at its next wait.
+                                if (ld_shared_volatile_u32(wctx.abort_smem) != 0u) break;
+                                if (global_timer_lo() - start > wctx.timeout_ns) {
+                                    st_shared_volatile_u32(wctx.abort_smem, 1u);
+                                    set_status(wctx.status, kStatusTimeout, (34u << 12) | (blockIdx.x & 0xFFFu));
+                                    break;
+                                }
+                            }
+                        }
+                    }
                 }
                 // Four chunks of 32 columns go through two 16 KiB staging buffers whose layout
                 // equals the accumulator's ([8 column quads][128 rows][4 floats]); one thread hands
@@ -755,25 +821,31 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     }
                 }
                 if (sem != nullptr && threadIdx.x == 256) {
-                    // Publish the previous tile once its four reductions are performed (the four of
-                    // this tile may still be in flight), so the warpgroup never waits for its own
-                    // latest additions.
-                    if (prev_sem != nullptr) {
-                        bulk_wait_group<4>();
-                        fence_proxy_async_all();
-                        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(prev_sem), "r"(prev_val) : "memory");
+                    // Publish the tile of two steps ago once its four reductions are performed (the
+                    // eight of the last two tiles may still be in flight).  The reductions are complete
+                    // -- performed in L2 -- before the counter is stored, so a block that reads the new
+                    // value can only add after them; a plain (relaxed) store is enough and, unlike a
+                    // release store, does not wait for this thread's other traffic.
+                    if (pend_sem[0] != nullptr) {
+                        bulk_wait_group<8>();
+                        asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(pend_sem[0]), "r"(pend_val[0]) : "memory");
                     }
-                    prev_sem = sem;
-                    prev_val = blk_index + 1;
+                    pend_sem[0] = pend_sem[1];
+                    pend_val[0] = pend_val[1];
+                    pend_sem[1] = sem;
+                    pend_val[1] = blk_index + 1;
                 }
                 PH_MARK(3);
             }
-            if (prev_sem != nullptr) {
-                // End of the work item: publish its last tile (thread 256 only holds prev_sem).
+            if (pend_sem[1] != nullptr) {
+                // End of the work item: publish its last tiles (only thread 256 holds any).
                 bulk_wait_group<0>();
                 fence_proxy_async_all();
-                asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(prev_sem), "r"(prev_val) : "memory");
-                prev_sem = nullptr;
+                if (pend_sem[0] != nullptr) {
+                    asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(pend_sem[0]), "r"(pend_val[0]) : "memory");
+                }
+                asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(pend_sem[1]), "r"(pend_val[1]) : "memory");
+                pend_sem[0] = pend_sem[1] = nullptr;
             }
         }
         if (threadIdx.x == 256) bulk_wait_group<0>();   // all reductions performed before the CTA ends
@@ -846,9 +918,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                         const uint32_t* src = g4 < 8 ? a : b;
                         const int o = (g4 & 7) * 4;
                         const float2 x0 = fma2(make_float2(__uint_as_float(src[o]), __uint_as_float(src[o + 1])),
-                                               make_float2(sl2, sl2), make_float2(-l.x, -l.y));
+                                               make_float2(sl2, sl2), make_float2(l.x, l.y));
                         const float2 x1 = fma2(make_float2(__uint_as_float(src[o + 2]), __uint_as_float(src[o + 3])),
-                                               make_float2(sl2, sl2), make_float2(-l.z, -l.w));
+                                               make_float2(sl2, sl2), make_float2(l.z, l.w));
                         // Part of the exponentials runs as a polynomial on the FMA pipe (see exp2_poly2).
                         const float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
                         const float2 p1 = ((kBwdExpPolyMask >> g4) & 1u)
@@ -902,12 +974,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     for (int g4 = 0; g4 < 8; ++g4) {
                         const float4 d = dsum[half * 8 + g4];
                         const uint32_t* src = half == 0 ? a : b;
-                        const float x0 = pr[half * 32 + 4 * g4 + 0] * (__uint_as_float(src[4 * g4 + 0]) - d.x);
-                        const float x1 = pr[half * 32 + 4 * g4 + 1] * (__uint_as_float(src[4 * g4 + 1]) - d.y);
-                        const float x2 = pr[half * 32 + 4 * g4 + 2] * (__uint_as_float(src[4 * g4 + 2]) - d.z);
-                        const float x3 = pr[half * 32 + 4 * g4 + 3] * (__uint_as_float(src[4 * g4 + 3]) - d.w);
-                        dsp[2 * g4] = pack_bf16x2(x0, x1);
-                        dsp[2 * g4 + 1] = pack_bf16x2(x2, x3);
+                        // dS = P * (dP - D) with D stored negated: one packed add and one packed multiply
+                        // per two elements.
+                        const float2 y0 = mul2(make_float2(pr[half * 32 + 4 * g4 + 0], pr[half * 32 + 4 * g4 + 1]),
+                                               add2(make_float2(__uint_as_float(src[4 * g4 + 0]),
+                                                                __uint_as_float(src[4 * g4 + 1])),
+                                                    make_float2(d.x, d.y)));
+                        const float2 y1 = mul2(make_float2(pr[half * 32 + 4 * g4 + 2], pr[half * 32 + 4 * g4 + 3]),
+                                               add2(make_float2(__uint_as_float(src[4 * g4 + 2]),
+                                                                __uint_as_float(src[4 * g4 + 3])),
+                                                    make_float2(d.z, d.w)));
+                        dsp[2 * g4] = pack_bf16x2(y0.x, y0.y);
+                        dsp[2 * g4 + 1] = pack_bf16x2(y1.x, y1.y);
                     }
                     PH_MARK(6);
 #pragma unroll
@@ -1011,8 +1089,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 }
 
 // ---------------------------------------------------------------------------------------
-// Preprocess: one warp per query row.  D = sum_d dO * O, LSE2 = LSE * log2(e) with -inf and
-// padding rows mapped to +inf (their P becomes exactly 0).
+// Preprocess: one warp per query row.  Writes -D = -sum_d dO * O and -LSE2 = -LSE * log2(e),
+// with -inf LSE and padding rows mapped to -inf (their P = exp2(s - inf) becomes exactly 0).
+// Both are stored negated because the main loop only ever subtracts them.  The same pass
+// clears the fp32 dQ accumulator.
 // ---------------------------------------------------------------------------------------
 struct BwdPreParams {
     const __nv_bfloat16* o;
@@ -1020,6 +1100,7 @@ struct BwdPreParams {
     const float* lse;
     float* lse2;
     float* dpsum;
+    float* dq_accum;     // zeroed here (each CTA clears the 16 KiB slab matching its 32 rows); may be null
     const int* cu_seqlens_q;
     int batch;
     int seqlen_q;
@@ -1040,6 +1121,22 @@ bwd_preprocess_kernel(const BwdPreParams p) {
     const int lane = threadIdx.x & 31;
     const int prow0 = (blockIdx.x * 8 + warp) * kPreRowsPerWarp;
     const int h = blockIdx.y;
+
+    // The fp32 dQ accumulator is heads_q * padded_q rows of 512 bytes: this CTA owns 32 rows'
+    // worth of it (one contiguous 16 KiB slab; which rows they are does not matter for zeroing).
+    if (p.dq_accum != nullptr) {
+        const long long slabs_per_head = (p.padded_q + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp);
+        const long long first_row = (static_cast<long long>(h) * slabs_per_head + blockIdx.x) * (8 * kPreRowsPerWarp);
+        const long long total_rows = static_cast<long long>(p.heads_q) * p.padded_q;
+        float4* base = reinterpret_cast<float4*>(p.dq_accum);
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+        // 32 rows x 32 float4 per row = 1024 float4; 256 threads x 4
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const long long idx = first_row * 32 + i * 256 + threadIdx.x;
+            if (idx < total_rows * 32) base[idx] = zero;
+        }
+    }
 
     uint2 ov[kPreRowsPerWarp], gv[kPreRowsPerWarp];
     long long lse_idx[kPreRowsPerWarp];
@@ -1094,7 +1191,7 @@ bwd_preprocess_kernel(const BwdPreParams p) {
         const int prow = prow0 + i;
         if (prow >= p.padded_q) continue;
         float d = 0.f;
-        float l2 = INFINITY;
+        float l2 = -INFINITY;
         if (valid[i]) {
             const float o0 = __uint_as_float(ov[i].x << 16), o1 = __uint_as_float(ov[i].x & 0xFFFF0000u);
             const float o2 = __uint_as_float(ov[i].y << 16), o3 = __uint_as_float(ov[i].y & 0xFFFF0000u);
@@ -1104,12 +1201,12 @@ bwd_preprocess_kernel(const BwdPreParams p) {
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, off);
             const float l = p.lse[lse_idx[i]];
-            l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+            l2 = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
         }
         if (lane == 0) {
             const long long out_idx = static_cast<long long>(h) * p.padded_q + prow;
             p.lse2[out_idx] = l2;
-            p.dpsum[out_idx] = d;
+            p.dpsum[out_idx] = -d;
         }
     }
 }

@@ -29,6 +29,15 @@ int current_device_info(DeviceInfo* info) {
     if (dev < 0 || dev >= 64) {
         return fail(B2A_ERR_CUDA, "device index %d out of range", dev);
     }
+    // The tensor-map encoder is a driver entry point and needs the device's primary context to
+    // be current on the calling thread.  A thread that has only ever used cached state (for
+    // example an autograd worker thread whose allocations all came from a caching allocator)
+    // may not have it bound yet; cudaSetDevice binds it.  Once per thread and device.
+    static thread_local bool bound[64] = {false};
+    if (!bound[dev]) {
+        B2A_CUDA_OK(cudaSetDevice(dev));
+        bound[dev] = true;
+    }
     std::lock_guard<std::mutex> lock(mu);
     if (!valid[dev]) {
         DeviceInfo d{};

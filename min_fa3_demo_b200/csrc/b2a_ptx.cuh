@@ -752,6 +752,20 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
     return d;
 }
 
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}\n"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
 // 2^x for two values on the FMA pipe instead of the special-function unit (16 ex2 per clock
 // per SM, which a 128x128 score tile keeps busy exactly as long as its two MMAs keep the tensor
 // pipe busy).  x = n + f with n = round(x) taken from the low mantissa bits of x + 1.5*2^23 and
