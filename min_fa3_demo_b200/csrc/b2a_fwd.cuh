@@ -2,7 +2,10 @@
 //
 // One persistent CTA per SM.  A work item is 256 query rows of one document and
 // one query head, processed as two 128-row tiles (A, B) that ping-pong on the
-// tensor core:
+// tensor core.  Where a document (or its last piece) has at most 128 rows left there is
+// no second row tile; the item then covers TWO query heads of the same K/V head for those
+// rows (tile A = head h, tile B = head h + 1, same K/V stream), so that the ping-pong --
+// and with it the overlap of softmax and tensor core -- is kept for short documents and tails.
 //
 //   warp  0-3   softmax warpgroup of tile A (one thread per query row)
 //   warp  4-7   softmax warpgroup of tile B
@@ -116,7 +119,22 @@ struct FwdWork {
     int n_full;    // ring mode: unmasked K/V blocks of other chunks that precede the own chunk
     int doc;       // ring mode: document index
     int half;      // ring mode: 0 = front half, 1 = back half of the local zigzag shard
+    int pair;      // 1: at most 128 rows left -> tiles A / B are heads `head`, `head + 1` of the same rows
+                   // (only the even head of each pair carries the work; the odd one's item is empty)
 };
+
+// First row (document-local) and query head of tile x of a work item.
+__device__ __forceinline__ int fwd_tile_row0(const FwdWork& wk, int x) {
+    return wk.m0 + (wk.pair ? 0 : x * kTileM);
+}
+__device__ __forceinline__ int fwd_tile_head(const FwdWork& wk, int x) {
+    return wk.head + (wk.pair ? x : 0);
+}
+
+// Whether a piece that starts at row m0 of a q_len-row document runs as a pair of heads.
+__device__ __forceinline__ int fwd_pair_mode(const FwdParams& p, int q_len, int m0) {
+    return (q_len - m0 <= kTileM && ((p.heads_q / p.heads_k) & 1) == 0) ? 1 : 0;
+}
 
 struct __align__(1024) FwdShared {
     uint8_t q[kFwdTilesPerCta][kTileBytes];
@@ -174,6 +192,7 @@ __device__ __forceinline__ FwdWork fwd_decode_work(const FwdParams& p, int w) {
         wk.m0 = e.z * kFwdRowsPerWork;
         wk.n_full = ring_full_chunks(p.causal, d.ring_size, d.ring_rank, e.y) * (d.half_len / kTileN);
         wk.lse_base = static_cast<long long>(wk.head) * p.lse_head_stride + wk.q_begin;
+        wk.pair = fwd_pair_mode(p, wk.q_len, wk.m0);
         return wk;
     }
     if (p.cu_seqlens_q == nullptr) {
@@ -198,13 +217,17 @@ __device__ __forceinline__ FwdWork fwd_decode_work(const FwdParams& p, int w) {
         wk.m0 = e.y * kFwdRowsPerWork;
         wk.lse_base = static_cast<long long>(wk.head) * p.lse_head_stride + wk.q_begin;
     }
+    wk.pair = fwd_pair_mode(p, wk.q_len, wk.m0);
     return wk;
 }
 
 // Number of K/V blocks tile `x` of the work item needs (0 when the tile has no
 // query row, or no visible key).
 __device__ __forceinline__ int fwd_num_kv_blocks(const FwdParams& p, const FwdWork& wk, int x) {
-    int row0 = wk.m0 + x * kTileM;
+    if (wk.pair && (wk.head & 1)) {
+        return 0;   // the even head of the pair carries both
+    }
+    int row0 = fwd_tile_row0(wk, x);
     if (row0 >= wk.q_len) {
         return 0;
     }
@@ -486,10 +509,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                         if (lane == 0) {
                             const uint32_t bar = smem_u32(&sh.q_full[x]);
                             const uint32_t dst = smem_u32(&sh.q[x][0]);
-                            const int row = wk.q_begin + wk.m0 + x * kTileM;
+                            const int row = wk.q_begin + fwd_tile_row0(wk, x);
                             mbar_arrive_expect_tx(bar, kTileBytes);
-                            tma_load_3d(dst, &map_q, bar, 0, wk.head, row);
-                            tma_load_3d(dst + kHalfTileBytes, &map_q, bar, 64, wk.head, row);
+                            tma_load_3d(dst, &map_q, bar, 0, fwd_tile_head(wk, x), row);
+                            tma_load_3d(dst + kHalfTileBytes, &map_q, bar, 64, fwd_tile_head(wk, x), row);
                         }
                     }
                 }
@@ -683,14 +706,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             }
             if (w < 0) break;
             const FwdWork wk = fwd_decode_work(p, w);
-            const int tile_row0 = wk.m0 + x * kTileM;
-            if (tile_row0 >= wk.q_len) continue;
+            const int tile_row0 = fwd_tile_row0(wk, x);
+            if (tile_row0 >= wk.q_len || (wk.pair && (wk.head & 1))) continue;
             const int nblk = fwd_num_kv_blocks(p, wk, x);
             const int row = tile_row0 + r;
             const bool row_valid = row < wk.q_len;
             const long long tok = static_cast<long long>(wk.q_begin) + row;
-            __nv_bfloat16* o_row = p.o + (tok * p.heads_q + wk.head) * kHeadDim;
-            float* lse_ptr = p.lse + wk.lse_base + row;
+            const int tile_head = fwd_tile_head(wk, x);
+            __nv_bfloat16* o_row = p.o + (tok * p.heads_q + tile_head) * kHeadDim;
+            float* lse_ptr = p.lse + wk.lse_base + static_cast<long long>(tile_head - wk.head) * p.lse_head_stride + row;
 
             // Key columns [0, col_limit) are visible to this row.
             int col_limit = wk.k_len;
