@@ -64,6 +64,33 @@ def measured_peaks():
     return FALLBACK_BF16_TFLOPS, 1400.0, "fallback"
 
 
+def kernel_source_digest() -> str:
+    """SHA-256 over the backward kernel's sources: ties a recorded ncu capture to the code it measured."""
+    import hashlib
+    h = hashlib.sha256()
+    for name in ("b2a_bwd.cuh", "b2a_bwd.cu", "b2a_ptx.cuh"):
+        h.update((ROOT / "min_fa3_demo_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()
+
+
+def recorded_traffic() -> dict:
+    """DRAM bytes per launch of the dominant kernel from the committed ncu capture
+    (profiles/bwd_kernel_traffic.json: read + write bytes of one launch at a smaller batch, scaled by
+    the batch ratio).  A number taken under a profiler cannot be produced inside this run, so it is a
+    record; it is reported only while the kernel sources still hash to what the capture measured,
+    otherwise ``traffic`` is null and the note says the record is stale."""
+    path = ROOT / "profiles" / "bwd_kernel_traffic.json"
+    if not path.exists():
+        return {"traffic": None, "traffic_note": "no ncu capture recorded"}
+    rec = json.loads(path.read_text())
+    if rec.get("kernel_source_sha256") != kernel_source_digest():
+        return {"traffic": None, "traffic_note": "recorded ncu capture is stale: the kernel sources changed since "
+                                                 f"{rec.get('captured_case')} was captured"}
+    return {"traffic": rec.get("dram_bytes_per_launch"),
+            "traffic_note": f"ncu capture of {rec.get('captured_case')} scaled x{rec.get('scale_to_bench_workload')} "
+                            "(traffic is proportional to the batch), kernel sources unchanged since"}
+
+
 # --------------------------------------------------------------------------------------
 # clocks
 # --------------------------------------------------------------------------------------
@@ -344,11 +371,12 @@ def run_cuda_arm(args) -> None:
         "kernel_ms": {"fwd_kernel": statistics.mean(fwd_ms) if fwd_ms else None,
                       "bwd_kernel": bwd_avg_ms,
                       "fwd_tflops": fwd_flops / (statistics.mean(fwd_ms) * 1e-3) / 1e12 if fwd_ms else None},
-        "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": achieved, "peak": sustained or burst,
-                     "peak_kind": f"{peak_kind} sustained cuBLAS bf16 (kernel timed inside a long step)",
-                     "unit": "TFLOP/s", "frac": achieved / (sustained or burst) if achieved else None,
-                     "frac_of_burst": achieved / burst if achieved else None,
-                     "traffic": None},
+        "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": achieved, "peak": burst,
+                     "peak_kind": f"{peak_kind} burst cuBLAS bf16 (the timed region is a fraction of a second, "
+                                  "well short of the seconds-long loop behind the sustained figure)",
+                     "unit": "TFLOP/s", "frac": achieved / burst if achieved else None,
+                     "frac_of_sustained": achieved / sustained if achieved and sustained else None,
+                     "traffic": None},  # filled from the recorded ncu capture below
         "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12 if e2e_ms else None, "unit": UNIT,
                 "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "api": "min_fa3_demo_b200.host_pipeline.HostPipeline.run (pinned host tensors in and out; "
@@ -359,9 +387,7 @@ def run_cuda_arm(args) -> None:
     }
     if world == 1 and not args.skip_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_record(args.cpu_seconds)
-    traffic_file = ROOT / "profiles" / "bwd_kernel_traffic.json"
-    if traffic_file.exists():
-        line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get("dram_bytes_per_launch")
+    line["roofline"].update(recorded_traffic())
     if ring_cp is not None:
         # The path that shards: reported beside the replica headline (whose `value` stays the
         # configuration-2 number at every N) and as a line of its own.
@@ -678,7 +704,7 @@ def ring_cp_leg(args, rank: int, local_rank: int, world: int, dev, dist) -> dict
 # --------------------------------------------------------------------------------------
 # Ring context-parallel workload (benchmark configuration 4)
 # --------------------------------------------------------------------------------------
-def run_ring_workload(args) -> None:
+def run_ring_workload(args, doc_lengths=None, emit=True):
     """One 131,072-token causal sequence (QH=32, KVH=8, d=128), zigzag-sharded over the N ranks;
     K/V of the other ranks is pulled over NVLink inside the attention launch.  Strong scaling:
     the problem is fixed, so whole-job TFLOPS = total FLOPs / max-over-ranks time.  Forward and
@@ -694,16 +720,20 @@ def run_ring_workload(args) -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
     from min_fa3_demo_b200 import balancer as bal
 
-    varlen = args.workload == "ring_varlen"
+    varlen = args.workload in ("ring_varlen", "ring_dataset")
     if varlen:
-        # Config 5: mixture-distributed documents, load-balanced placement on sub-rings.
+        # Config 5: mixture-distributed documents, load-balanced placement on sub-rings
+        # (or the document lengths of one dataset-shaped batch, given by the caller).
         qh, kvh = 64, 8
-        lengths = bal.sample_mixture_lengths(0, target_tokens=args.ring_tokens)
-        lengths[-1] -= sum(lengths) - args.ring_tokens      # last document truncated to fill
+        if doc_lengths is not None:
+            lengths = list(doc_lengths)
+        else:
+            lengths = bal.sample_mixture_lengths(0, target_tokens=args.ring_tokens)
+            lengths[-1] -= sum(lengths) - args.ring_tokens      # last document truncated to fill
         if world > 1:
             plan = bal.assign_hierarchical_rings(lengths, world, True)
             glens, sizes, starts = plan.global_lengths, plan.ring_sizes, plan.ring_starts
@@ -907,7 +937,63 @@ def run_ring_workload(args) -> None:
                        "achieved_gbs_over_fwd_kernel": ingress / (fm * 1e-3) / 1e9 if world > 1 else 0.0},
             "gpu_launches": 4 * args.steps, "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
+        if emit:
+            print(json.dumps(line), flush=True)
+        else:
+            line["flops"] = f_flops + b_flops
+            return line
+    if world > 1 and emit:
+        dist.destroy_process_group()
+    return None
+
+
+def run_ring_dataset(args) -> None:
+    """Dataset-shaped context-parallel runs (the reference's benchmark_dataset protocol,
+    benchmark_logs/*/benchmark_dataset.log: packed batches of ~131,072 tokens whose document
+    lengths follow a dataset's length histogram, placed by the load balancer on hierarchical
+    sub-rings; reported as TFLOPS/GPU weighted over the cases, i.e. total FLOPs / total time).
+    The histogram comes from a file in the reference's format (``--length-buckets``, e.g. the
+    reference checkout's dataset/sequence_length_buckets.json, with ``--dataset`` naming the entry)
+    or, without one, from the synthetic log-normal / Pareto mixture stand-in."""
+    import torch.distributed as dist
+
+    from min_fa3_demo_b200 import balancer as bal
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.length_buckets:
+        tables = bal.load_length_buckets(args.length_buckets)
+        if args.dataset not in tables:
+            raise SystemExit(f"--dataset {args.dataset!r} is not in {args.length_buckets} (has: {sorted(tables)})")
+        counts, source = tables[args.dataset], f"{args.dataset} ({args.length_buckets})"
+    else:
+        counts, source = bal.synthetic_length_buckets(), "synthetic log-normal/Pareto mixture histogram"
+    cases = bal.generate_dataset_length_cases(counts, args.ring_tokens, args.dataset_seed, args.cases)
+    records = []
+    for lengths in cases:
+        rec = run_ring_workload(args, doc_lengths=lengths, emit=False)
+        if rank == 0:
+            records.append(rec)
+    if rank == 0:
+        flops = sum(r["flops"] for r in records)
+        seconds = sum(r["ms_per_step"] for r in records) * 1e-3
+        fwd_s = sum(r["fwd_ms"] for r in records) * 1e-3
+        burst, sustained, peak_kind = measured_peaks()
+        value = flops / seconds / 1e12
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": seconds * 1e3 / len(records), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"ring_dataset_T{args.ring_tokens}_QH64_KVH8_D128", "length_histogram": source,
+                       "cases": len(records), "seed": args.dataset_seed,
+                       "documents_per_case": [r["config"]["documents"] for r in records],
+                       "weighting": "total FLOPs / total time over the cases (forward + backward)"},
+            "tflops_per_gpu": value / world,
+            "fwd_tflops_per_gpu": sum(r["flops"] for r in records) * (4.0 / 14.0) / fwd_s / 1e12 / world,
+            "pct_of_bf16_peak": {f"{peak_kind}_burst": 100.0 * value / world / burst},
+            "per_case_tflops_per_gpu": [r["tflops_per_gpu"] for r in records],
+            "per_case_placement": [r["config"]["placement"] for r in records],
+            "gpu_launches": 4 * args.steps * len(records), "clocks": records[-1]["clocks"]}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -1008,10 +1094,17 @@ def main() -> None:
                         help="time budget of the CPU baseline sample (N=1 only)")
     parser.add_argument("--batch", type=int, default=None,
                         help="override the per-GPU batch (smaller cases for profiler captures)")
-    parser.add_argument("--workload", choices=("bshd", "varlen", "ring", "ring_varlen"), default="bshd",
+    parser.add_argument("--workload", choices=("bshd", "varlen", "ring", "ring_varlen", "ring_dataset"), default="bshd",
                         help="bshd: config 2 replicas (default); varlen: config 3 (65,536 packed tokens, 1 GPU); "
                              "ring: config 4, one long causal sequence over N ranks; ring_varlen: config 5, "
-                             "131,072 packed tokens placed on hierarchical sub-rings over N ranks")
+                             "131,072 packed tokens placed on hierarchical sub-rings over N ranks; ring_dataset: "
+                             "several such batches whose document lengths follow a dataset length histogram")
+    parser.add_argument("--length-buckets", default=None,
+                        help="ring_dataset: length-histogram file in the reference's format "
+                             "(dataset/sequence_length_buckets.json of the reference checkout)")
+    parser.add_argument("--dataset", default="arxiv", help="ring_dataset: entry of the histogram file")
+    parser.add_argument("--cases", type=int, default=4, help="ring_dataset: packed batches to run")
+    parser.add_argument("--dataset-seed", type=int, default=0)
     parser.add_argument("--non-causal", action="store_true", help="bshd workload without the causal mask")
     parser.add_argument("--ring-tokens", type=int, default=131072)
     parser.add_argument("--ring-comm-sm", type=int, default=8)
@@ -1025,7 +1118,12 @@ def main() -> None:
     parser.add_argument("--e2e-head-groups", type=int, default=2,
                         help="chunks per batch element in the host-buffer pipeline (must divide the KV heads)")
     parser.add_argument("--skip-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--print-kernel-digest", action="store_true",
+                        help="print the hash of the backward kernel sources (recorded beside an ncu traffic capture) and exit")
     args = parser.parse_args()
+    if args.print_kernel_digest:
+        print(kernel_source_digest())
+        return
     if args.non_causal:
         WORKLOAD["causal"] = False
         WORKLOAD["name"] = WORKLOAD["name"].replace("bshd_causal", "bshd_noncausal")
@@ -1034,6 +1132,8 @@ def main() -> None:
         WORKLOAD["name"] = WORKLOAD["name"].replace("_B4_", f"_B{args.batch}_")
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "ring_dataset":
+        run_ring_dataset(args)
     elif args.workload in ("ring", "ring_varlen"):
         run_ring_workload(args)
     elif args.workload == "varlen":

@@ -292,6 +292,105 @@ def sample_mixture_lengths(seed: int, target_tokens: int = 131072, max_len: int 
     return lengths
 
 
+# --------------------------------------------------------------------------------------
+# Dataset-shaped length sampling (reference: balancer/sampler.py:28-174)
+# --------------------------------------------------------------------------------------
+LENGTH_BUCKET_SIZE = 256
+
+
+def load_length_buckets(path) -> dict:
+    """Reads a length-histogram file in the reference's format (``dataset/sequence_length_buckets.json``:
+    ``bucket_size`` 256, ``max_sequence_tokens`` 131072, ``interval`` "(lower, upper]",
+    ``overflow_policy`` "clamp_to_last_bucket", and per dataset ``sample_count`` plus 512
+    ``bucket_counts``) and returns ``{dataset: tuple(counts)}``.  The checks and their messages follow
+    balancer/sampler.py:28-91.  The file itself belongs to the reference checkout and is not shipped here."""
+    import json
+    from pathlib import Path
+
+    path = Path(path)
+    try:
+        payload = json.loads(path.read_text(encoding="utf-8"))
+    except (OSError, json.JSONDecodeError) as exc:
+        raise RuntimeError(f"failed to load dataset bucket statistics from {path}") from exc
+    if not isinstance(payload, dict):
+        raise RuntimeError(f"bucket statistics in {path} must be a JSON object")
+    if payload.get("bucket_size") != LENGTH_BUCKET_SIZE:
+        raise RuntimeError(f"bucket_size in {path} must be {LENGTH_BUCKET_SIZE}, got {payload.get('bucket_size')!r}")
+    if payload.get("max_sequence_tokens") != MAX_SEQUENCE_TOKENS:
+        raise RuntimeError(f"max_sequence_tokens in {path} must be {MAX_SEQUENCE_TOKENS}, "
+                           f"got {payload.get('max_sequence_tokens')!r}")
+    if payload.get("interval") != "(lower, upper]":
+        raise RuntimeError(f"interval in {path} must be '(lower, upper]'")
+    if payload.get("overflow_policy") != "clamp_to_last_bucket":
+        raise RuntimeError(f"overflow_policy in {path} must be 'clamp_to_last_bucket'")
+    datasets = payload.get("datasets")
+    if not isinstance(datasets, dict) or not datasets:
+        raise RuntimeError(f"datasets in {path} must be a non-empty JSON object")
+    expected = MAX_SEQUENCE_TOKENS // LENGTH_BUCKET_SIZE
+    result = {}
+    for name, stats in datasets.items():
+        counts = stats.get("bucket_counts") if isinstance(stats, dict) else None
+        if not isinstance(counts, list) or len(counts) != expected:
+            raise RuntimeError(f"bucket_counts for {name!r} in {path} must contain {expected} entries")
+        if any(type(c) is not int or c < 0 for c in counts):
+            raise RuntimeError(f"bucket_counts for {name!r} in {path} must be non-negative integers")
+        if sum(counts) != stats.get("sample_count"):
+            raise RuntimeError(f"bucket_counts for {name!r} in {path} sum to {sum(counts)}, "
+                               f"expected sample_count={stats.get('sample_count')!r}")
+        result[name] = tuple(counts)
+    return result
+
+
+def synthetic_length_buckets(seed: int = 0, samples: int = 200000) -> Tuple[int, ...]:
+    """A stand-in histogram for machines without the reference's dataset statistics: bucket counts of
+    the 70/30 log-normal / Pareto mixture of benchmark configuration 5 (the same distribution
+    ``sample_mixture_lengths`` draws from), in the file format's 512 buckets of 256 tokens."""
+    rng = np.random.default_rng(seed)
+    heavy = rng.random(samples) >= 0.7
+    lengths = np.where(heavy, 8192.0 * (1.0 + rng.pareto(1.1, samples)),
+                       rng.lognormal(math.log(2000.0), 1.0, samples))
+    lengths = np.clip(np.rint(lengths), 1, MAX_SEQUENCE_TOKENS).astype(np.int64)
+    buckets = np.minimum((lengths + LENGTH_BUCKET_SIZE - 1) // LENGTH_BUCKET_SIZE,
+                         MAX_SEQUENCE_TOKENS // LENGTH_BUCKET_SIZE) - 1
+    return tuple(int(c) for c in np.bincount(buckets, minlength=MAX_SEQUENCE_TOKENS // LENGTH_BUCKET_SIZE))
+
+
+def generate_dataset_length_cases(bucket_counts: Sequence[int], target_tokens: int, seed: int, num_cases: int
+                                  ) -> List[List[int]]:
+    """``num_cases`` packed batches drawn from one ``random.Random(seed)`` stream, exactly as the
+    reference sampler does (balancer/sampler.py:126-174): a bucket is drawn with probability
+    proportional to its count, its upper bound is the sampled length, the last document of a batch is
+    cut to the remaining budget, and every length is rounded up by the ring-aware tiers
+    (``align_sequence_length``).  With the reference's histogram and the same seed the batches equal
+    the reference's."""
+    import random
+
+    if num_cases <= 0:
+        raise ValueError(f"num_cases must be positive, got {num_cases}")
+    if target_tokens <= 0:
+        raise ValueError(f"target_tokens must be positive, got {target_tokens}")
+    counts = list(bucket_counts)
+    total = sum(counts)
+    if total <= 0:
+        raise RuntimeError("bucket counts must contain at least one sample")
+    rng = random.Random(seed)
+    cases = []
+    for _ in range(num_cases):
+        lengths, remaining = [], target_tokens
+        while remaining > 0:
+            draw, cumulative, idx = rng.randrange(total), 0, 0
+            for idx, count in enumerate(counts):
+                cumulative += count
+                if draw < cumulative:
+                    break
+            sampled = (idx + 1) * LENGTH_BUCKET_SIZE
+            length = align_sequence_length(min(sampled, remaining, MAX_SEQUENCE_TOKENS))
+            lengths.append(length)
+            remaining = max(remaining - length, 0)
+        cases.append(lengths)
+    return cases
+
+
 def local_layout(workload: HybridWorkload, rank: int) -> Tuple[List[int], List[int]]:
     """This rank's local document lengths (0 for rings it is not part of) and their cumulative
     offsets, in the placement's document order — the ``cu_seqlens`` a rank passes to the

@@ -41,6 +41,22 @@ def main() -> None:
     out.write_text(json.dumps(cases))
     print(f"{out.name}: {out.stat().st_size} bytes, {len(cases)} cases")
 
+    # The reference's dataset-shaped sampler (balancer/sampler.py:126-174) run on a SYNTHETIC
+    # histogram (the mixture stand-in of this repository, not the reference's dataset statistics):
+    # its per-dataset count table is swapped for the synthetic one for the duration of the call.
+    from balancer import sampler as ref_sampler
+
+    from min_fa3_demo_b200.balancer import synthetic_length_buckets
+    counts = synthetic_length_buckets(seed=5, samples=50000)
+    ref_sampler._DATASET_BUCKET_COUNTS["synthetic"] = counts
+    sampled = []
+    for target, seed, num in ((131072, 0, 3), (131072, 7, 2), (65536, 1, 2), (16384, 3, 2)):
+        sampled.append({"target_tokens": target, "seed": seed,
+                        "cases": ref_sampler.generate_dataset_length_cases("synthetic", target, seed, num)})
+    out = Path(__file__).resolve().parent / "sampler_reference.json"
+    out.write_text(json.dumps({"histogram_seed": 5, "histogram_samples": 50000, "runs": sampled}))
+    print(f"{out.name}: {out.stat().st_size} bytes")
+
 
 if __name__ == "__main__":
     main()

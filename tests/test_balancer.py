@@ -109,3 +109,53 @@ def test_random_inputs_give_legal_plans(lengths, world, causal):
     for rank in range(world):
         lens, cu = bal.local_layout(plan, rank)
         assert cu[-1] == plan.rank_tokens[rank]
+
+
+# --------------------------------------------------------------------------------------
+# Dataset-shaped sampling (reference: balancer/sampler.py:28-174)
+# --------------------------------------------------------------------------------------
+def test_dataset_sampler_matches_recorded_reference_sampler():
+    """Same histogram + same seed -> the batches of the reference's ``generate_dataset_length_cases``
+    (recorded by tests/golden/make_balancer_golden.py on a synthetic histogram)."""
+    import json
+    from pathlib import Path
+
+    golden = json.loads((Path(__file__).resolve().parent / "golden" / "sampler_reference.json").read_text())
+    counts = bal.synthetic_length_buckets(seed=golden["histogram_seed"], samples=golden["histogram_samples"])
+    assert len(counts) == 512 and sum(counts) == golden["histogram_samples"]
+    for run in golden["runs"]:
+        got = bal.generate_dataset_length_cases(counts, run["target_tokens"], run["seed"], len(run["cases"]))
+        assert got == run["cases"]
+        for lengths in got:
+            assert sum(lengths) >= run["target_tokens"]
+            assert all(n % 256 == 0 and 0 < n <= bal.MAX_SEQUENCE_TOKENS for n in lengths)
+
+
+def test_length_bucket_file_format_is_the_reference_format(tmp_path):
+    import json
+
+    counts = [0] * 512
+    counts[3], counts[40], counts[511] = 5, 2, 1
+    good = {"bucket_size": 256, "max_sequence_tokens": 131072, "interval": "(lower, upper]",
+            "overflow_policy": "clamp_to_last_bucket", "tokenizer": "none",
+            "datasets": {"toy": {"sample_count": 8, "bucket_counts": counts}}}
+    path = tmp_path / "buckets.json"
+    path.write_text(json.dumps(good))
+    loaded = bal.load_length_buckets(path)
+    assert loaded == {"toy": tuple(counts)}
+    cases = bal.generate_dataset_length_cases(loaded["toy"], 32768, 0, 2)
+    assert len(cases) == 2 and all(sum(c) >= 32768 for c in cases)
+    for key, value, fragment in (("bucket_size", 128, "bucket_size"), ("interval", "[lower, upper)", "interval"),
+                                 ("overflow_policy", "drop", "overflow_policy")):
+        bad = dict(good)
+        bad[key] = value
+        path.write_text(json.dumps(bad))
+        with pytest.raises(RuntimeError, match=fragment):
+            bal.load_length_buckets(path)
+    bad = json.loads(json.dumps(good))
+    bad["datasets"]["toy"]["sample_count"] = 9
+    path.write_text(json.dumps(bad))
+    with pytest.raises(RuntimeError, match="sum to 8"):
+        bal.load_length_buckets(path)
+    with pytest.raises(RuntimeError, match="failed to load"):
+        bal.load_length_buckets(tmp_path / "missing.json")
