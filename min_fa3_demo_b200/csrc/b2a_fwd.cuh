@@ -91,6 +91,7 @@ struct FwdParams {
     uint8_t* arena_v;
     int* kv_flags;                     // per 128-row arena block: 1 once K and V have landed
     int* copy_done;                    // number of copy CTAs that have finished all their tasks
+    unsigned long long* stats;         // optional [2]: query tiles visited, K/V tile reads (counted by the kernel)
     // ---- ring step mode: CTAs [num_comp, gridDim.x) first copy two flat buffers (another rank's
     // K and V) into local prefetch buffers, then join the attention work queue.  0 otherwise.
     const uint8_t* prefetch_src[2];
@@ -560,6 +561,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             uint32_t q_cnt[2] = {0, 0};
             uint32_t p_cnt[2] = {0, 0};
             bool ok = true;
+            unsigned long long tile_visits = 0, kv_tile_reads = 0;   // CTA-local totals for p.stats
             PH_DECL(8)   // 0 other, 1 wait p_full, 2 issue PV, 3 wait K, 4 issue S
             const uint32_t s_tmem[2] = {tmem_base + 0u, tmem_base + 128u};
             const uint32_t o_tmem[2] = {tmem_base + 256u, tmem_base + 384u};
@@ -600,6 +602,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     if (nblk[x] > 0) {
                         ok = ok && mbar_wait(wctx, smem_u32(&sh.q_full[x]), q_cnt[x] & 1u, 5);
                         ++q_cnt[x];
+                        tile_visits += 1;
+                        kv_tile_reads += static_cast<unsigned long long>(nblk[x]);
                     }
                 }
                 if (!ok) break;
@@ -678,6 +682,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                     }
                     if (j > 0) ++kv_it;
                 }
+            }
+            // Each CTA submits its two totals once (reference: include/min_fa3_kernel.h:618-625).
+            if (p.stats != nullptr && lane == 0 && tile_visits != 0) {
+                atomicAdd(p.stats, tile_visits);
+                atomicAdd(p.stats + 1, kv_tile_reads);
             }
             PH_PRINT("fwd mma", 5);
         }

@@ -89,7 +89,6 @@ int b2a_ring_fwd(const b2a_ring_fwd_args* a, void* cuda_stream) {
     // Work list: (document, half, 256-row piece), most expensive first.
     struct Entry { int4 e; int cost; };
     std::vector<Entry> entries;
-    long long qo_visits = 0, kv_reads = 0;
     for (int d : plan.doc_order) {
         const RingDoc& doc = plan.docs[d];
         const int hb = doc.half_len / kTileN;
@@ -99,10 +98,6 @@ int b2a_ring_fwd(const b2a_ring_fwd_args* a, void* cuda_stream) {
             for (int pair = 0; pair * 2 < hb; ++pair) {
                 const int t_last = std::min(hb - 1, pair * 2 + 1);
                 entries.push_back({make_int4(d, h, pair, 0), n_full + (causal ? t_last + 1 : 0)});
-                for (int t = pair * 2; t <= t_last; ++t) {
-                    qo_visits += a->heads_q;
-                    kv_reads += static_cast<long long>(a->heads_q) * (n_full + (causal ? t + 1 : 0));
-                }
             }
         }
     }
@@ -115,8 +110,7 @@ int b2a_ring_fwd(const b2a_ring_fwd_args* a, void* cuda_stream) {
     B2A_CUDA_OK(cudaMemsetAsync(hdr, 0, sizeof(WorkspaceHeader), stream));
     B2A_CUDA_OK(cudaMemsetAsync(ws + lay.flags_off, 0, lay.flag_count * sizeof(int), stream));
     if (a->stats != nullptr) {
-        const long long st[2] = {qo_visits, kv_reads};
-        B2A_CUDA_OK(cudaMemcpyAsync(a->stats, st, sizeof(st), cudaMemcpyHostToDevice, stream));
+        B2A_CUDA_OK(cudaMemsetAsync(a->stats, 0, 2 * sizeof(long long), stream));   // the kernel counts
     }
     if (entries.empty()) return B2A_OK;   // this rank holds no tokens
 
@@ -173,6 +167,7 @@ int b2a_ring_fwd(const b2a_ring_fwd_args* a, void* cuda_stream) {
     p.arena_v = static_cast<uint8_t*>(a->arena_v);
     p.kv_flags = reinterpret_cast<int*>(ws + lay.flags_off);
     p.copy_done = &hdr->reserved;
+    p.stats = reinterpret_cast<unsigned long long*>(a->stats);
 
     const int comm = p.comm_task_count > 0 ? a->num_comm_sm : 0;
     int grid = a->num_comp_sm + comm;
