@@ -56,6 +56,17 @@ def step_flops(w=WORKLOAD):
     return 4.0 * unit, 10.0 * unit
 
 
+def workload_config(world: int) -> dict:
+    """The ``config`` record of the headline workload; the same dict in both arms."""
+    w = WORKLOAD
+    fwd, bwd = step_flops()
+    return {"workload": w["name"], "batch_per_gpu": w["batch"], "seq_len": w["seqlen"], "heads_q": w["heads_q"],
+            "heads_k": w["heads_k"], "head_dim": 128, "causal": w["causal"],
+            "parallelism": f"{world} independent replica(s), no data-path collective",
+            "l2": "inputs larger than L2 (1.7 GB of tensors per step vs 126 MB L2)",
+            "flops_per_step_per_gpu": fwd + bwd}
+
+
 def measured_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -228,7 +239,9 @@ def run_reference_arm(args) -> None:
         "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": (fwd + bwd) / (value * 1e12) * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD["name"], "note": "ms_per_step extrapolates the sampled rate to the full workload"},
+        "config": workload_config(args.gpus),
+        "sampled": "each step times a bounded sample of the workload's (batch, KV-head) groups on the host cores; "
+                   "ms_per_step extrapolates the sampled rate to the full workload",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -359,11 +372,7 @@ def run_cuda_arm(args) -> None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": w["name"], "batch_per_gpu": b, "seq_len": s, "heads_q": qh,
-                   "heads_k": kvh, "head_dim": 128, "causal": causal,
-                   "parallelism": f"{world} independent replica(s), no data-path collective",
-                   "l2": "inputs larger than L2 (1.7 GB of tensors per step vs 126 MB L2)",
-                   "flops_per_step_per_gpu": flops},
+        "config": workload_config(world),
         "tflops_per_gpu": value / world,
         "pct_of_bf16_peak": {f"{peak_kind}_burst": 100.0 * value / world / burst,
                              f"{peak_kind}_sustained": 100.0 * value / world / sustained if sustained else None,

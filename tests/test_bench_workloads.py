@@ -45,3 +45,30 @@ def test_ring_varlen_documents_place_on_eight_ranks():
     for rank in range(8):
         lens, cu = bal.local_layout(plan, rank)
         assert cu[-1] == plan.rank_tokens[rank] and all(n % 128 == 0 for n in lens)
+
+
+def test_recorded_dram_traffic_is_tied_to_the_kernel_sources(tmp_path, monkeypatch):
+    """The DRAM traffic in the bench line comes from a committed ncu capture; it is only reported
+    while the backward kernel's sources still hash to what the capture measured."""
+    import json
+
+    digest = bench.kernel_source_digest()
+    assert len(digest) == 64
+    record = json.loads((ROOT / "profiles" / "bwd_kernel_traffic.json").read_text())
+    assert record["dram_bytes_per_launch"] == record["scale_to_bench_workload"] * (
+        record["dram_bytes_read_captured"] + record["dram_bytes_write_captured"])
+    got = bench.recorded_traffic()
+    if record["kernel_source_sha256"] == digest:
+        assert got["traffic"] == record["dram_bytes_per_launch"]
+    else:
+        assert got["traffic"] is None and "stale" in got["traffic_note"]
+    # a changed source makes the record stale
+    monkeypatch.setattr(bench, "kernel_source_digest", lambda: "0" * 64)
+    stale = bench.recorded_traffic()
+    assert stale["traffic"] is None and "stale" in stale["traffic_note"]
+
+
+def test_both_arms_report_the_same_config_record():
+    cfg = bench.workload_config(1)
+    assert cfg["workload"] == bench.WORKLOAD["name"] and cfg["flops_per_step_per_gpu"] == sum(bench.step_flops())
+    assert bench.workload_config(8)["parallelism"].startswith("8 independent")
