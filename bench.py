@@ -284,7 +284,7 @@ def run_cuda_arm(args) -> None:
 
     def step_resident():
         out, lse = min_fa3_op.forward(q, k, v, causal, return_lse=True)
-        return out, min_fa3_op.backward(dout, q, k, v, out, lse, causal)
+        return out, min_fa3_op.backward(dout, q, k, v, out, lse, causal, deterministic=w.get("deterministic", False))
 
     def barrier():
         if world > 1:
@@ -1115,6 +1115,8 @@ def main() -> None:
     parser.add_argument("--cases", type=int, default=4, help="ring_dataset: packed batches to run")
     parser.add_argument("--dataset-seed", type=int, default=0)
     parser.add_argument("--non-causal", action="store_true", help="bshd workload without the causal mask")
+    parser.add_argument("--deterministic", action="store_true",
+                        help="bshd workload with the backward's fixed dQ accumulation order (bit-identical repeats)")
     parser.add_argument("--ring-tokens", type=int, default=131072)
     parser.add_argument("--ring-comm-sm", type=int, default=8)
     parser.add_argument("--ring-impl", choices=("fused", "allgather"), default="fused",
@@ -1136,6 +1138,9 @@ def main() -> None:
     if args.non_causal:
         WORKLOAD["causal"] = False
         WORKLOAD["name"] = WORKLOAD["name"].replace("bshd_causal", "bshd_noncausal")
+    if args.deterministic:
+        WORKLOAD["deterministic"] = True
+        WORKLOAD["name"] += "_deterministic_dq"
     if args.batch is not None:
         WORKLOAD["batch"] = args.batch
         WORKLOAD["name"] = WORKLOAD["name"].replace("_B4_", f"_B{args.batch}_")

@@ -249,6 +249,14 @@ size_t b2a_ring_fwd_workspace_bytes(int32_t batch, int32_t world_size, int32_t r
  * and all ranks must have synchronised before the call.  Replaces
  * `forward_varlen_mega_ring` (csrc/mega_ring_min_fa3_varlen_ring_bindings.cu:304) including
  * the hierarchical sub-rings (include/min_fa3_mega_ring_hierarchy.h:13-33).
+ *
+ * Host work per call (this entry point and b2a_ring_bwd): the work list and the copy tasks are
+ * built on the host from the `*_host` arrays and uploaded with one cudaMemcpyAsync from an
+ * ordinary (pageable) std::vector.  The runtime stages such a copy before the call returns, so
+ * the vector may be freed at once, but the copy is why these two calls may not be captured into
+ * a CUDA graph and why they are not fully asynchronous to the host (the host blocks until the
+ * staging copy is taken, not until the kernels end).  Callers that need capture or no host
+ * work use the plain entry points (b2a_fwd_noalloc, b2a_fwd, b2a_bwd) per ring step.
  */
 int b2a_ring_fwd(const b2a_ring_fwd_args* args, void* cuda_stream);
 

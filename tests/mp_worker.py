@@ -399,11 +399,11 @@ def case_empty_rank(rank, world, dev):
             print("empty_rank: needs at least 2 ranks, skipped", flush=True)
         return
     qh, kvh, causal = 4, 2, True
-    members = world - 1 if world - 1 in (1, 2, 4) else (4 if world == 8 else 1)
+    members = 1 << ((world - 1).bit_length() - 1)                 # largest power of two below world
     docs = []
     if members > 1:
         docs.append((members * 512, members, 0))
-    docs += [(384, 1, 0), (256, 1, max(members - 1, 0))]          # the last rank gets nothing
+    docs += [(384 if r % 2 == 0 else 256, 1, r) for r in range(world - 1)]   # the last rank gets nothing
     q, k, v, dout, cu, odocs = build_problem(world, rank, docs, qh, kvh, causal, BASE_SEED + 31)
     assert (rank == world - 1) == (q.size(0) == 0), "test layout: exactly the last rank is empty"
     cap = 2048
