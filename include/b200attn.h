@@ -291,6 +291,10 @@ typedef struct b2a_ring_bwd_args {
     int32_t is_causal;
     int32_t num_comp_sm;
     int32_t num_comm_sm;
+    int32_t kv_resident;                 /* non-zero: the arena still holds every remote K/V block this rank's
+                                            queries see, left there by b2a_ring_fwd on the same metadata and
+                                            K/V; nothing is pulled again and all CTAs compute from the start.
+                                            0 (the reference's behaviour): the backward pulls them itself. */
     void* workspace;
     size_t workspace_bytes;
 } b2a_ring_bwd_args;

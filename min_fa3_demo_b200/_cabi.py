@@ -153,6 +153,7 @@ class RingBwdArgs(Structure):
         ("is_causal", c_int32),
         ("num_comp_sm", c_int32),
         ("num_comm_sm", c_int32),
+        ("kv_resident", c_int32),
         ("workspace", c_void_p),
         ("workspace_bytes", c_size_t),
     ]

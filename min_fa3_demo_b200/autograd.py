@@ -140,7 +140,8 @@ class _RingFn(torch.autograd.Function):
     def backward(ctx, dout):
         q, k, v, out, lse, cu = ctx.saved_tensors
         ring: RingAttention = ctx.ring
-        if ring._generation != ctx.generation:
+        resident = ring._generation == ctx.generation   # the forward's remote blocks are still in the arena
+        if not resident:
             # Another forward has used the arena since this call's forward (several layers or
             # micro-batches share the object, or activation checkpointing re-ran a forward): put
             # this call's K/V back.  Every rank sees the same sequence of calls, so all of them
@@ -152,7 +153,7 @@ class _RingFn(torch.autograd.Function):
             cu_seqlens_q_host=ctx.cu_host, cu_seqlens_k_host=ctx.cu_host, remote_k=ring.arena_k,
             remote_v=ring.arena_v, remote_dk_accum=ring.acc_k, remote_dv_accum=ring.acc_v,
             remote_dkv_completion=ring.done, num_comp_sm=ring.num_comp_sm, num_comm_sm=ring.num_comm_sm,
-            is_causal=ring.is_causal, **ctx.meta)
+            is_causal=ring.is_causal, kv_resident=resident, **ctx.meta)
         return dq, dk[:ctx.kv_rows], dv[:ctx.kv_rows], None, None, None, None, None
 
 

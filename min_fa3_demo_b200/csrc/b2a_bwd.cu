@@ -177,7 +177,7 @@ int b2a_bwd(const b2a_bwd_args* a, void* cuda_stream) {
         pre.lse_batch_stride = static_cast<long long>(a->heads_q) * a->seqlen_q;
     }
     {
-        dim3 grid((lay.padded_q + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp), a->heads_q);
+        dim3 grid((lay.padded_q + kPreRows - 1) / kPreRows);
         bwd_preprocess_kernel<<<grid, 256, 0, stream>>>(pre);
         B2A_CUDA_OK(cudaGetLastError());
     }
@@ -320,7 +320,10 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
     if (rc != B2A_OK) return rc;
     B2A_REQUIRE(a->cu_seqlens_q_host[a->batch] == a->total_q, "cu_seqlens_q_host[-1] must equal total_q");
     B2A_REQUIRE(a->local_total_k == a->total_q, "local_total_k must equal total_q for context-parallel backward");
-    B2A_REQUIRE(plan.comm_tasks.empty() || a->num_comm_sm > 0,
+    // kv_resident: the forward left every remote block this rank needs in the arena; no copy
+    // tasks, no block flags, and the CTAs past num_comp_sm compute from the start.
+    const bool pull = !plan.comm_tasks.empty() && a->kv_resident == 0;
+    B2A_REQUIRE(!pull || a->num_comm_sm > 0,
                 "num_comm_sm must be positive when documents are sharded over more than one rank");
     for (int r = 0; r < world; ++r) {
         B2A_REQUIRE(a->dk_accum_peer[r] && a->dv_accum_peer[r] && a->completion_peer[r],
@@ -381,7 +384,7 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
         memcpy(host.data(), plan.docs.data(), plan.docs.size() * sizeof(RingDoc));
         int4* w = reinterpret_cast<int4*>(host.data() + (lay.work_off - lay.docs_off));
         for (size_t i = 0; i < entries.size(); ++i) w[i] = entries[i].e;
-        if (!plan.comm_tasks.empty()) {
+        if (pull) {
             memcpy(host.data() + (lay.tasks_off - lay.docs_off), plan.comm_tasks.data(),
                    plan.comm_tasks.size() * sizeof(int2));
         }
@@ -402,7 +405,7 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
         pre.padded_q = a->total_q;
         pre.lse_head_stride = a->total_q;
         pre.lse_batch_stride = 0;
-        dim3 pgrid((a->total_q + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp), a->heads_q);
+        dim3 pgrid((a->total_q + kPreRows - 1) / kPreRows);
         bwd_preprocess_kernel<<<pgrid, 256, 0, stream>>>(pre);
         B2A_CUDA_OK(cudaGetLastError());
 
@@ -437,7 +440,7 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
         p.ring_docs = reinterpret_cast<const RingDoc*>(ws + lay.docs_off);
         p.ring_work = reinterpret_cast<const int4*>(ws + lay.work_off);
         p.comm_tasks = reinterpret_cast<const int2*>(ws + lay.tasks_off);
-        p.comm_task_count = static_cast<int>(plan.comm_tasks.size());
+        p.comm_task_count = pull ? static_cast<int>(plan.comm_tasks.size()) : 0;
         p.num_comp = a->num_comp_sm;
         p.my_rank = rank;
         p.kv_row_bytes = a->heads_k * kHeadDim * 2;
@@ -458,7 +461,9 @@ int b2a_ring_bwd(const b2a_ring_bwd_args* a, void* cuda_stream) {
 
         rc = configure_bwd_kernel(dev);
         if (rc != B2A_OK) return rc;
-        const int comm = p.comm_task_count > 0 ? a->num_comm_sm : 0;
+        // Without copies the extra CTAs are attention CTAs like the others (sharded documents
+        // only: a launch that never had copy tasks keeps its grid).
+        const int comm = plan.comm_tasks.empty() ? 0 : a->num_comm_sm;
         const int grid = a->num_comp_sm + comm;
         profile_mark(B2A_KERNEL_BWD, false, stream);
         bwd_kernel<<<grid, kBwdThreads, kRingBwdSmemBytes, stream>>>(map_q, map_k, map_v, map_do, p);

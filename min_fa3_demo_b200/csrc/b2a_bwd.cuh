@@ -475,7 +475,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                 ok = mbar_wait(wctx, smem_u32(&sh.kv_empty), (item_cnt & 1u) ^ 1u, 2);
                 if (!ok) break;
                 ++item_cnt;
-                if (p.ring_docs != nullptr && wk.owner != p.my_rank) {
+                if (p.ring_docs != nullptr && wk.owner != p.my_rank && p.comm_task_count > 0) {
                     ok = flag_wait(wctx, p.kv_flags + wk.k_row / kTileN, 23);
                     if (!ok) break;
                     fence_proxy_async_all();
@@ -1110,103 +1110,109 @@ struct BwdPreParams {
     long long lse_batch_stride;
 };
 
-constexpr int kPreRowsPerWarp = 4;   // rows per warp: their loads are all in flight together
+constexpr int kPreRows = 8;          // padded rows per CTA, all heads: one contiguous stretch of O / dO
+constexpr int kPreItemsPerWarp = 4;  // (row, head) items a warp loads together
 
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const BwdPreParams p) {
-    // grid: (ceil(padded_q / 32), heads_q); 8 warps per CTA, kPreRowsPerWarp consecutive padded
-    // rows per warp.  The kernel is pure streaming (reads O and dO once); several rows per warp
-    // keep enough loads in flight to approach the memory bandwidth.
+    // grid: padded_q / kPreRows CTAs of 8 warps.  A CTA owns kPreRows consecutive padded rows and
+    // every head of them, so (for consecutive tokens) it streams one contiguous stretch of
+    // kPreRows * heads_q * 256 bytes of O and of dO: consecutive warps read consecutive 256-byte
+    // (row, head) items, kPreItemsPerWarp of them in flight per warp.
+    __shared__ long long s_tok[kPreRows];   // packed token index of the padded row, -1 for padding rows
+    __shared__ long long s_lse[kPreRows];   // LSE index of the row without the head term
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int prow0 = (blockIdx.x * 8 + warp) * kPreRowsPerWarp;
-    const int h = blockIdx.y;
+    const int prow_base = blockIdx.x * kPreRows;
 
-    // The fp32 dQ accumulator is heads_q * padded_q rows of 512 bytes: this CTA owns 32 rows'
-    // worth of it (one contiguous 16 KiB slab; which rows they are does not matter for zeroing).
-    if (p.dq_accum != nullptr) {
-        const long long slabs_per_head = (p.padded_q + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp);
-        const long long first_row = (static_cast<long long>(h) * slabs_per_head + blockIdx.x) * (8 * kPreRowsPerWarp);
-        const long long total_rows = static_cast<long long>(p.heads_q) * p.padded_q;
-        float4* base = reinterpret_cast<float4*>(p.dq_accum);
-        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-        // 32 rows x 32 float4 per row = 1024 float4; 256 threads x 4
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const long long idx = first_row * 32 + i * 256 + threadIdx.x;
-            if (idx < total_rows * 32) base[idx] = zero;
-        }
-    }
-
-    uint2 ov[kPreRowsPerWarp], gv[kPreRowsPerWarp];
-    long long lse_idx[kPreRowsPerWarp];
-    bool valid[kPreRowsPerWarp];
-#pragma unroll
-    for (int i = 0; i < kPreRowsPerWarp; ++i) {
-        const int prow = prow0 + i;
-        valid[i] = false;
-        lse_idx[i] = 0;
-        ov[i] = make_uint2(0u, 0u);
-        gv[i] = make_uint2(0u, 0u);
-        if (prow >= p.padded_q) continue;
-        // Locate the document that owns this padded row.
-        int doc = -1, q_begin = 0, q_len = 0, pad_begin = 0;
-        if (p.cu_seqlens_q == nullptr) {
-            const int per = ((p.seqlen_q + 127) / 128) * 128;
-            doc = prow / per;
-            pad_begin = doc * per;
-            q_begin = doc * p.seqlen_q;
-            q_len = p.seqlen_q;
-            if (doc >= p.batch) doc = -1;
-        } else {
-            // Binary search over padded begins (monotone in doc).
-            int lo = 0, hi = p.batch - 1;
-            while (lo < hi) {
-                int mid = (lo + hi + 1) >> 1;
-                if (bwd_padded_begin(p.cu_seqlens_q[mid], mid) <= prow) lo = mid; else hi = mid - 1;
-            }
-            doc = lo;
-            q_begin = p.cu_seqlens_q[doc];
-            q_len = p.cu_seqlens_q[doc + 1] - q_begin;
-            pad_begin = bwd_padded_begin(q_begin, doc);
-            if (prow < pad_begin) doc = -1;
-        }
-        const int r = prow - pad_begin;
-        if (doc >= 0 && r < q_len) {
-            valid[i] = true;
-            const long long tok = static_cast<long long>(q_begin) + r;
-            const long long base = (tok * p.heads_q + h) * kHeadDim + lane * 4;
-            ov[i] = *reinterpret_cast<const uint2*>(p.o + base);
-            gv[i] = *reinterpret_cast<const uint2*>(p.dout + base);
+    if (threadIdx.x < kPreRows) {
+        const int prow = prow_base + threadIdx.x;
+        long long tok = -1, lse_base = 0;
+        if (prow < p.padded_q) {
+            // Locate the document that owns this padded row.
+            int doc, q_begin, q_len, pad_begin;
             if (p.cu_seqlens_q == nullptr) {
-                lse_idx[i] = static_cast<long long>(doc) * p.lse_batch_stride +
-                             static_cast<long long>(h) * p.lse_head_stride + r;
+                const int per = ((p.seqlen_q + 127) / 128) * 128;
+                doc = prow / per;
+                pad_begin = doc * per;
+                q_begin = doc * p.seqlen_q;
+                q_len = p.seqlen_q;
+                if (doc >= p.batch) doc = -1;
             } else {
-                lse_idx[i] = static_cast<long long>(h) * p.lse_head_stride + tok;
+                // Binary search over padded begins (monotone in doc).
+                int lo = 0, hi = p.batch - 1;
+                while (lo < hi) {
+                    int mid = (lo + hi + 1) >> 1;
+                    if (bwd_padded_begin(p.cu_seqlens_q[mid], mid) <= prow) lo = mid; else hi = mid - 1;
+                }
+                doc = lo;
+                q_begin = p.cu_seqlens_q[doc];
+                q_len = p.cu_seqlens_q[doc + 1] - q_begin;
+                pad_begin = bwd_padded_begin(q_begin, doc);
+                if (prow < pad_begin) doc = -1;
+            }
+            const int r = prow - pad_begin;
+            if (doc >= 0 && r < q_len) {
+                tok = static_cast<long long>(q_begin) + r;
+                lse_base = p.cu_seqlens_q == nullptr ? static_cast<long long>(doc) * p.lse_batch_stride + r : tok;
             }
         }
+        s_tok[threadIdx.x] = tok;
+        s_lse[threadIdx.x] = lse_base;
     }
+
+    // The fp32 dQ accumulator is heads_q * padded_q rows of 512 bytes: this CTA clears the
+    // contiguous slab of kPreRows * heads_q rows with its index (which rows of which head they
+    // are does not matter for zeroing; the slabs of all CTAs tile the accumulator).
+    if (p.dq_accum != nullptr) {
+        const long long slab_f4 = static_cast<long long>(kPreRows) * p.heads_q * 32;   // float4 per slab
+        const long long total_f4 = static_cast<long long>(p.heads_q) * p.padded_q * 32;
+        float4* base = reinterpret_cast<float4*>(p.dq_accum) + blockIdx.x * slab_f4;
+        const long long room = total_f4 - blockIdx.x * slab_f4;
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (long long idx = threadIdx.x; idx < slab_f4 && idx < room; idx += 256) base[idx] = zero;
+    }
+    __syncthreads();
+
+    const int items = kPreRows * p.heads_q;
+    for (int i0 = warp * kPreItemsPerWarp; i0 < items; i0 += 8 * kPreItemsPerWarp) {
+        uint2 ov[kPreItemsPerWarp], gv[kPreItemsPerWarp];
+        float lv[kPreItemsPerWarp];
 #pragma unroll
-    for (int i = 0; i < kPreRowsPerWarp; ++i) {
-        const int prow = prow0 + i;
-        if (prow >= p.padded_q) continue;
-        float d = 0.f;
-        float l2 = -INFINITY;
-        if (valid[i]) {
-            const float o0 = __uint_as_float(ov[i].x << 16), o1 = __uint_as_float(ov[i].x & 0xFFFF0000u);
-            const float o2 = __uint_as_float(ov[i].y << 16), o3 = __uint_as_float(ov[i].y & 0xFFFF0000u);
-            const float g0 = __uint_as_float(gv[i].x << 16), g1 = __uint_as_float(gv[i].x & 0xFFFF0000u);
-            const float g2 = __uint_as_float(gv[i].y << 16), g3 = __uint_as_float(gv[i].y & 0xFFFF0000u);
-            d = o0 * g0 + o1 * g1 + o2 * g2 + o3 * g3;
+        for (int j = 0; j < kPreItemsPerWarp; ++j) {
+            const int it = i0 + j;
+            ov[j] = make_uint2(0u, 0u);
+            gv[j] = make_uint2(0u, 0u);
+            lv[j] = -INFINITY;
+            if (it >= items) continue;
+            const int row = it / p.heads_q, h = it - row * p.heads_q;
+            const long long tok = s_tok[row];
+            if (tok < 0) continue;
+            const long long base = (tok * p.heads_q + h) * kHeadDim + lane * 4;
+            ov[j] = __ldcs(reinterpret_cast<const uint2*>(p.o + base));
+            gv[j] = __ldcs(reinterpret_cast<const uint2*>(p.dout + base));
+            if (lane == 0) lv[j] = p.lse[s_lse[row] + static_cast<long long>(h) * p.lse_head_stride];
+        }
+#pragma unroll
+        for (int j = 0; j < kPreItemsPerWarp; ++j) {
+            const int it = i0 + j;
+            if (it >= items) continue;
+            const int row = it / p.heads_q, h = it - row * p.heads_q;
+            const int prow = prow_base + row;
+            if (prow >= p.padded_q) continue;
+            const float o0 = __uint_as_float(ov[j].x << 16), o1 = __uint_as_float(ov[j].x & 0xFFFF0000u);
+            const float o2 = __uint_as_float(ov[j].y << 16), o3 = __uint_as_float(ov[j].y & 0xFFFF0000u);
+            const float g0 = __uint_as_float(gv[j].x << 16), g1 = __uint_as_float(gv[j].x & 0xFFFF0000u);
+            const float g2 = __uint_as_float(gv[j].y << 16), g3 = __uint_as_float(gv[j].y & 0xFFFF0000u);
+            float d = o0 * g0 + o1 * g1 + o2 * g2 + o3 * g3;   // 0 for padding rows
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, off);
-            const float l = p.lse[lse_idx[i]];
-            l2 = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
-        }
-        if (lane == 0) {
-            const long long out_idx = static_cast<long long>(h) * p.padded_q + prow;
-            p.lse2[out_idx] = l2;
-            p.dpsum[out_idx] = -d;
+            if (lane == 0) {
+                const float l = lv[j];
+                const long long out_idx = static_cast<long long>(h) * p.padded_q + prow;
+                p.lse2[out_idx] = (l == -INFINITY) ? -INFINITY : -l * kLog2e;
+                p.dpsum[out_idx] = -d;
+            }
         }
     }
 }
@@ -1232,7 +1238,10 @@ struct BwdPostParams {
 
 __global__ void __launch_bounds__(128)
 bwd_postprocess_kernel(const BwdPostParams p) {
-    __shared__ float tile[kTileM][64 + 4];
+    // bf16 staging of the whole 128 x 128 tile; a pitch of 66 words keeps the 8-byte column-chunk
+    // stores of 16 consecutive rows on distinct banks.
+    constexpr int kPitch = kHeadDim + 4;
+    __shared__ __align__(8) __nv_bfloat16 tile[kTileM * kPitch];
     const int pad_tile = blockIdx.x;
     const int h = blockIdx.y;
     const int pad_tiles = p.padded_q / kTileM;
@@ -1265,31 +1274,25 @@ bwd_postprocess_kernel(const BwdPostParams p) {
         ? static_cast<long long>(h) * pad_tiles + pad_tile
         : static_cast<long long>(h) * p.tile_head_stride + static_cast<long long>(pad_tile) * p.tile_row_stride;
     const float4* src = reinterpret_cast<const float4*>(p.dq_accum + tile_index * kDqTileFloats);
-    // src[chunk * 128 + row] holds columns 4*chunk .. 4*chunk+3 of `row`.  Two passes of 64
-    // columns each keep the transposition buffer inside static shared memory.
-    const int sub = threadIdx.x & 7;
-    for (int half = 0; half < 2; ++half) {
-        for (int chunk = 0; chunk < 16; ++chunk) {
-            const float4 v = src[(half * 16 + chunk) * kTileM + threadIdx.x];
-            float* dst = &tile[threadIdx.x][chunk * 4];
-            dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+    // src[chunk * 128 + row] holds columns 4*chunk .. 4*chunk+3 of `row`: thread = row reads its 32
+    // chunks (each warp instruction a contiguous 512 bytes), scales, rounds and stages them.
+#pragma unroll 8
+    for (int chunk = 0; chunk < 32; ++chunk) {
+        const float4 v = __ldcs(src + chunk * kTileM + threadIdx.x);
+        uint2 o;
+        o.x = pack_bf16x2(v.x * p.scale, v.y * p.scale);
+        o.y = pack_bf16x2(v.z * p.scale, v.w * p.scale);
+        *reinterpret_cast<uint2*>(&tile[threadIdx.x * kPitch + chunk * 4]) = o;
+    }
+    __syncthreads();
+    // One warp writes one whole 256-byte row per instruction (32 lanes x 8 bytes).
+    const int lane = threadIdx.x & 31;
+    for (int rr = threadIdx.x >> 5; rr < kTileM; rr += 4) {
+        if (r0 + rr < q_len) {
+            const uint2 o = *reinterpret_cast<const uint2*>(&tile[rr * kPitch + lane * 4]);
+            const long long tok = static_cast<long long>(q_begin) + r0 + rr;
+            *reinterpret_cast<uint2*>(p.dq + (tok * p.heads_q + h) * kHeadDim + lane * 4) = o;
         }
-        __syncthreads();
-        // 8 threads x 16 bytes cover the 128-byte half row; 16 rows per pass.
-        for (int rr = threadIdx.x >> 3; rr < kTileM; rr += 16) {
-            if (r0 + rr < q_len) {
-                const float* sp = &tile[rr][sub * 8];
-                uint4 o;
-                o.x = pack_bf16x2(sp[0] * p.scale, sp[1] * p.scale);
-                o.y = pack_bf16x2(sp[2] * p.scale, sp[3] * p.scale);
-                o.z = pack_bf16x2(sp[4] * p.scale, sp[5] * p.scale);
-                o.w = pack_bf16x2(sp[6] * p.scale, sp[7] * p.scale);
-                const long long tok = static_cast<long long>(q_begin) + r0 + rr;
-                *reinterpret_cast<uint4*>(p.dq + (tok * p.heads_q + h) * kHeadDim + half * 64 +
-                                          sub * 8) = o;
-            }
-        }
-        __syncthreads();
     }
 }
 

@@ -46,7 +46,9 @@ varlen_plan_kernel(int kind, const int* __restrict__ cu_q, const int* __restrict
                    int causal, int2* __restrict__ work_list, int* __restrict__ num_entries,
                    int max_entries_cap) {
     __shared__ int bucket[kCostBuckets];
+    __shared__ int warp_sum[32];
     __shared__ int total;
+    static_assert(kCostBuckets == 2 * kPlanThreads, "the scan gives every thread two buckets");
     for (int i = threadIdx.x; i < kCostBuckets; i += kPlanThreads) bucket[i] = 0;
     if (threadIdx.x == 0) total = 0;
     __syncthreads();
@@ -63,15 +65,36 @@ varlen_plan_kernel(int kind, const int* __restrict__ cu_q, const int* __restrict
     }
     __syncthreads();
 
-    // Exclusive scan over buckets from the most expensive down (single thread: 2048 adds).
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int c = kCostBuckets - 1; c >= 0; --c) {
-            int n = bucket[c];
-            bucket[c] = run;
-            run += n;
+    // Exclusive scan over the buckets from the most expensive down: thread t owns the two
+    // buckets at descending positions 2t and 2t+1; warp scan, then a scan of the 32 warp sums.
+    {
+        const int t = threadIdx.x, lane = t & 31, wid = t >> 5;
+        const int c_hi = kCostBuckets - 1 - 2 * t, c_lo = c_hi - 1;
+        const int n_hi = bucket[c_hi], n_lo = bucket[c_lo];
+        const int mine = n_hi + n_lo;
+        int incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += up;
         }
-        *num_entries = min(total, max_entries_cap);
+        if (lane == 31) warp_sum[wid] = incl;
+        __syncthreads();
+        if (wid == 0) {
+            const int ws = warp_sum[lane];
+            int wincl = ws;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xFFFFFFFFu, wincl, d);
+                if (lane >= d) wincl += up;
+            }
+            warp_sum[lane] = wincl - ws;
+        }
+        __syncthreads();
+        const int excl = warp_sum[wid] + incl - mine;
+        bucket[c_hi] = excl;
+        bucket[c_lo] = excl + n_hi;
+        if (t == 0) *num_entries = min(total, max_entries_cap);
     }
     __syncthreads();
 

@@ -467,8 +467,8 @@ def backward_varlen_mega_ring(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_
                               remote_k: TKParallelTensor, remote_v: TKParallelTensor,
                               remote_dk_accum: TKParallelTensor, remote_dv_accum: TKParallelTensor,
                               remote_dkv_completion: TKParallelTensor, num_comp_sm: int, num_comm_sm: int,
-                              global_seqlens_host, ring_sizes_host, ring_starts_host, is_causal: bool = True
-                              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                              global_seqlens_host, ring_sizes_host, ring_starts_host, is_causal: bool = True,
+                              kv_resident: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Context-parallel backward of ``forward_varlen_mega_ring`` (reference:
     ``backward_varlen_mega_ring``, csrc/backward/min_fa3_bwd_bindings.cu:375-722; causal like the
     reference by default, the non-causal ring is accepted too).
@@ -477,7 +477,12 @@ def backward_varlen_mega_ring(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_
     accumulators ``remote_dk_accum`` / ``remote_dv_accum`` (at least ``dkv_accum_numel(KVH,
     logical_rank_capacity, B)`` floats, the reference's sizing rule) and the one-element int32
     ``remote_dkv_completion`` counter must be zeroed, and all ranks synchronised, before every
-    call.  Returns ``dq [total_q, QH, 128]`` and compact ``dk, dv [local_total_k, KVH, 128]``."""
+    call.  Returns ``dq [total_q, QH, 128]`` and compact ``dk, dv [local_total_k, KVH, 128]``.
+
+    ``kv_resident`` (not in the reference, whose backward always pulls the remote K/V again):
+    pass True when this rank's arena still holds what ``forward_varlen_mega_ring`` left there on
+    the same metadata and K/V -- nothing crosses NVLink for K/V then and every CTA computes from
+    the start.  With the default the call is self-contained like the reference's."""
     max_seqlen_q, max_seqlen_k = int(max_seqlen_q), int(max_seqlen_k)
     num_comp_sm, num_comm_sm = int(num_comp_sm), int(num_comm_sm)
     world, rank, cap, batch, local_total_k = _validate_backward_mega_ring(
@@ -511,6 +516,7 @@ def backward_varlen_mega_ring(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_
     a.heads_q, a.heads_k, a.head_dim = q.size(1), k.size(1), 128
     a.is_causal = int(bool(is_causal))
     a.num_comp_sm, a.num_comm_sm = num_comp_sm, num_comm_sm
+    a.kv_resident = int(bool(kv_resident))
     a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
     with torch.cuda.device(q.device):
         _cabi.check(lib.b2a_ring_bwd(ctypes.byref(a), _stream_ptr(q.device)))

@@ -303,7 +303,9 @@ def case_ring_steps(rank, world, dev):
 
 def case_mega_ring_bwd(rank, world, dev):
     """dQ / dK / dV of the context-parallel backward against fp32 autograd over the global
-    documents (dense reference as in ...backward_multi_rank.py:95-122, oracle-side)."""
+    documents (dense reference as in ...backward_multi_rank.py:95-122, oracle-side).  The first
+    repetition pulls the remote K/V again like the reference's backward, the second one works on
+    what the forward left in the arena (``kv_resident``)."""
     qh, kvh = 8, 2
     sm = torch.cuda.get_device_properties(dev).multi_processor_count
     for causal in (True, False):
@@ -330,7 +332,7 @@ def case_mega_ring_bwd(rank, world, dev):
                 dd, qd, rk.data_, rv.data_, out, lse, cud, cud, mx, mx, cu_seqlens_q_host=cu,
                 cu_seqlens_k_host=cu, remote_k=rk, remote_v=rv, remote_dk_accum=acc_k, remote_dv_accum=acc_v,
                 remote_dkv_completion=done, num_comp_sm=sm - 8, num_comm_sm=8, global_seqlens_host=g,
-                ring_sizes_host=s, ring_starts_host=st, is_causal=causal)
+                ring_sizes_host=s, ring_starts_host=st, is_causal=causal, kv_resident=(rep == 1))
             torch.cuda.synchronize()
             try:
                 min_fa3_op.check_last_status("backward_varlen_mega_ring")
