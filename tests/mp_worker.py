@@ -156,6 +156,8 @@ def ring_docs_for(world: int, causal: bool = True):
     if world >= 4:
         half = world // 2
         docs += [(half * 512, half, 0), (half * 256, half, half)]
+    if world >= 8:
+        docs += [(2 * 256, 2, 2), (2 * 512, 2, world - 2)]
     if world >= 2:
         docs += [(512, 1, 0), (256, 1, world - 1), (128, 1, 1 % world)]
     else:

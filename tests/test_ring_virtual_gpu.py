@@ -6,7 +6,8 @@ only reads the slices the owners wrote before the launch), so the W launches sim
 after the other on one stream.  This executes, on a single-GPU machine, everything a real
 multi-GPU forward executes except the NVLink hop: the copy CTAs (peer -> shared -> own arena),
 the per-block ready flags and their bounded waits, the zigzag virtual block map, hierarchical
-sub-rings, and the one-chunk layout of unmasked rings (shards of 384 rows).
+sub-rings (8 virtual ranks: rings of 8, 4, 2 and 1), and the one-chunk layout of unmasked rings
+(shards of 384 rows).
 
 The backward is not emulated this way: it ends with a wait for the other ranks' completion
 signals, which would never come from launches queued behind it on the same GPU.
@@ -76,7 +77,7 @@ def expected_stats(docs, rank, causal):
 
 
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_virtual_ranks_forward_matches_oracle(world, causal):
     lib = _cabi.load()
     dev = torch.device("cuda", 0)
