@@ -964,6 +964,100 @@ def run_ring_workload(args, doc_lengths=None, emit=True):
     return None
 
 
+def run_ring_virtual(args) -> None:
+    """Forward of the ring workload with the ranks emulated on ONE GPU: every virtual rank owns a
+    K/V arena on the same device and gets the others' as its peer pointers; the W launches run one
+    after the other (the forward never waits for another rank's launch).  Everything a real
+    multi-GPU forward executes runs except the NVLink hop, so the per-rank times separate what the
+    work lists and the copy CTAs cost from what the link costs.  T(1) is the same sequence through
+    ``forward_varlen`` on the same GPU."""
+    import min_fa3_op
+    from min_fa3_demo_b200 import _cabi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lib = _cabi.load()
+    world, tokens, comm = args.virtual_ranks, args.ring_tokens, args.ring_comm_sm
+    qh, kvh = 32, 8
+    local = tokens // world
+    cap = local
+    gen = torch.Generator(device=dev).manual_seed(1)
+
+    def rand(rows, heads):
+        return torch.randn(rows, heads, 128, device=dev, generator=gen).to(torch.bfloat16)
+    arenas_k = [rand(world * cap, kvh) for _ in range(world)]
+    arenas_v = [rand(world * cap, kvh) for _ in range(world)]
+    q = rand(local, qh)
+    out = torch.empty_like(q)
+    lse = torch.empty(qh, local, device=dev)
+    cu = torch.tensor([0, local], dtype=torch.int32)
+    meta = [torch.tensor([x], dtype=torch.int32) for x in (tokens, world, 0)]
+    sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    nbytes = lib.b2a_ring_fwd_workspace_bytes(1, world, cap, local)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    warm, steps = max(args.warmup, 3), args.steps
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.mark_begin()
+    per_rank = {}
+    for r in range(world):
+        a = _cabi.RingFwdArgs()
+        a.q, a.out, a.lse = q.data_ptr(), out.data_ptr(), lse.data_ptr()
+        a.arena_k, a.arena_v = arenas_k[r].data_ptr(), arenas_v[r].data_ptr()
+        for x in range(world):
+            a.peer_k[x], a.peer_v[x] = arenas_k[x].data_ptr(), arenas_v[x].data_ptr()
+        a.cu_seqlens_q_host = cu.data_ptr()
+        a.global_seqlens_host, a.ring_sizes_host, a.ring_starts_host = (m.data_ptr() for m in meta)
+        a.batch, a.world_size, a.rank, a.rank_kv_capacity = 1, world, r, cap
+        a.total_q, a.heads_q, a.heads_k, a.head_dim, a.is_causal = local, qh, kvh, 128, 1
+        a.num_comp_sm, a.num_comm_sm = sm - comm, comm
+        a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+        times = []
+        for it in range(warm + steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _cabi.check(lib.b2a_ring_fwd(ctypes.byref(a), stream))
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= warm:
+                times.append(e0.elapsed_time(e1))
+        _cabi.check(lib.b2a_check_status(ctypes.c_void_p(ws.data_ptr()), None))
+        per_rank[r] = statistics.mean(times)
+    del arenas_k, arenas_v
+    torch.cuda.empty_cache()
+    q1, k1, v1 = rand(tokens, qh), rand(tokens, kvh), rand(tokens, kvh)
+    cu1 = torch.tensor([0, tokens], dtype=torch.int32)
+    cu1d = cu1.to(dev)
+    times = []
+    for it in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        min_fa3_op.forward_varlen(q1, k1, v1, cu1d, cu1d, tokens, tokens, True, cu_seqlens_q_host=cu1,
+                                  cu_seqlens_k_host=cu1)
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 1:
+            times.append(e0.elapsed_time(e1))
+    sampler.mark_end()
+    clocks = sampler.stop()
+    t1 = statistics.mean(times)
+    slowest = max(per_rank.values())
+    flops = 4.0 * qh * 128 * tokens * (tokens + 1) / 2
+    print(json.dumps({
+        "metric": "forward attention TFLOPS (causal FLOPs) of the slowest virtual rank x ranks", "unit": "TFLOPS",
+        "value": flops / (slowest * 1e-3) / 1e12 / world, "n_gpus": 1, "steps": steps, "warmup": warm,
+        "ms_per_step": slowest, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"ring_virtual_fwd_causal_S{tokens}_QH{qh}_KVH{kvh}_D128", "virtual_ranks": world,
+                   "copy_ctas": comm, "l2": "inputs larger than L2"},
+        "fwd_ms_per_rank": per_rank, "t1_fwd_ms": t1, "t1_over_ranks_ms": t1 / world,
+        "efficiency_fwd_slowest_rank": t1 / world / slowest,
+        "gpu_launches": world * (warm + steps) + 3, "clocks": clocks}), flush=True)
+
+
 def run_ring_dataset(args) -> None:
     """Dataset-shaped context-parallel runs (the reference's benchmark_dataset protocol,
     benchmark_logs/*/benchmark_dataset.log: packed batches of ~131,072 tokens whose document
@@ -1119,11 +1213,15 @@ def main() -> None:
                         help="time budget of the CPU baseline sample (N=1 only)")
     parser.add_argument("--batch", type=int, default=None,
                         help="override the per-GPU batch (smaller cases for profiler captures)")
-    parser.add_argument("--workload", choices=("bshd", "varlen", "ring", "ring_varlen", "ring_dataset"), default="bshd",
+    parser.add_argument("--workload", choices=("bshd", "varlen", "ring", "ring_varlen", "ring_dataset", "ring_virtual"),
+                        default="bshd",
                         help="bshd: config 2 replicas (default); varlen: config 3 (65,536 packed tokens, 1 GPU); "
                              "ring: config 4, one long causal sequence over N ranks; ring_varlen: config 5, "
                              "131,072 packed tokens placed on hierarchical sub-rings over N ranks; ring_dataset: "
-                             "several such batches whose document lengths follow a dataset length histogram")
+                             "several such batches whose document lengths follow a dataset length histogram; "
+                             "ring_virtual: the ring forward with --virtual-ranks ranks emulated on one GPU")
+    parser.add_argument("--virtual-ranks", type=int, default=4, choices=(2, 4, 8),
+                        help="ring_virtual: number of emulated ranks")
     parser.add_argument("--length-buckets", default=None,
                         help="ring_dataset: length-histogram file in the reference's format "
                              "(dataset/sequence_length_buckets.json of the reference checkout)")
@@ -1164,6 +1262,8 @@ def main() -> None:
         run_reference_arm(args)
     elif args.workload == "ring_dataset":
         run_ring_dataset(args)
+    elif args.workload == "ring_virtual":
+        run_ring_virtual(args)
     elif args.workload in ("ring", "ring_varlen"):
         run_ring_workload(args)
     elif args.workload == "varlen":
