@@ -447,6 +447,68 @@ def _bound(e_low_precision: float) -> float:
     return 2.0 * max(e_low_precision, 2.0 ** -9)
 
 
+def _ring_workload_parity(rank, world, dev, dist, glens, sizes, starts, q, k, v, dout, out, lse, dq, cap):
+    """Sampled-row check of a context-parallel run at its full size: for up to three of this
+    rank's documents (largest, smallest, median) a few local query rows, all heads, O / LSE / dQ
+    against plain fp32 PyTorch over the document's K/V gathered from its ring members (checker
+    plumbing: an all_gather of the local K/V).  Bound: 2x the error of the same computation with
+    bf16 scores / probabilities, LSE 1e-3.  The verdict is voted over all ranks."""
+    kvh = k.size(1)
+
+    def layout(r):
+        lens = [n // g if st <= r < st + g else 0 for n, g, st in zip(glens, sizes, starts)]
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        return lens, cu
+    pad_k = torch.zeros(cap, kvh, 128, dtype=torch.bfloat16, device=dev)
+    pad_v = torch.zeros_like(pad_k)
+    pad_k[:k.size(0)], pad_v[:v.size(0)] = k, v
+    if world > 1:
+        gk = torch.empty(world, cap, kvh, 128, dtype=torch.bfloat16, device=dev)
+        gv = torch.empty_like(gk)
+        dist.all_gather_into_tensor(gk, pad_k)
+        dist.all_gather_into_tensor(gv, pad_v)
+    else:
+        gk, gv = pad_k[None], pad_v[None]
+    lens, cu = layout(rank)
+    mine = sorted((d for d in range(len(glens)) if lens[d] > 0), key=lambda d: glens[d])
+    picks_d = sorted({mine[0], mine[len(mine) // 2], mine[-1]}) if mine else []
+    worst = {"o": 0.0, "lse": 0.0, "dq": 0.0}
+    checked = 0
+    for d in picks_d:
+        g, st, n = sizes[d], starts[d], lens[d]
+        parts_k, parts_v, parts_pos = [], [], []
+        for m in range(st, st + g):
+            off = layout(m)[1][d]
+            parts_k.append(gk[m, off:off + n])
+            parts_v.append(gv[m, off:off + n])
+            parts_pos.append(_zigzag_positions(g, m - st, n, dev))
+        kf, vf, kpos = torch.cat(parts_k), torch.cat(parts_v), torch.cat(parts_pos)
+        qpos = _zigzag_positions(g, rank - st, n, dev)
+        rows = torch.tensor(sorted({0, n // 2 - 1, n // 2, n - 1, (104729 * (rank + 3)) % n, (7919 * (d + 5)) % n}),
+                            device=dev)
+        sel = rows + cu[d]
+        ref_o, ref_l, ref_g = _dense_rows(q[sel], kf, vf, qpos[rows], kpos, dout[sel])
+        low_o, _low_l, low_g = _dense_rows(q[sel], kf, vf, qpos[rows], kpos, dout[sel], low_precision=True)
+        b_o = _bound((low_o - ref_o).abs().max().item())
+        b_q = _bound((low_g[0].float() - ref_g[0]).abs().max().item())
+        worst["o"] = max(worst["o"], (out[sel].float() - ref_o).abs().max().item() / b_o)
+        worst["lse"] = max(worst["lse"], (lse[:, sel] - ref_l).abs().max().item() / 1e-3)
+        worst["dq"] = max(worst["dq"], (dq[sel].float() - ref_g[0]).abs().max().item() / b_q)
+        checked += rows.numel()
+    ok = all(x <= 1.0 for x in worst.values())
+    t = torch.tensor([1.0 if ok else 0.0, -worst["o"], -worst["lse"], -worst["dq"], -float(checked)], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return {"pass": bool(t[0].item() == 1.0),
+            "rule": "O / LSE / dQ of sampled local rows (all heads) of up to three documents per rank against fp32 "
+                    "PyTorch on the GPU; bound 2x the error of the same computation with bf16 scores / "
+                    "probabilities, LSE 1e-3; worst ratio over all ranks",
+            "worst_err_over_bound": {"o": -t[1].item(), "lse": -t[2].item(), "dq": -t[3].item()},
+            "rows_checked_max_rank": int(-t[4].item())}
+
+
 def ring_cp_leg(args, rank: int, local_rank: int, world: int, dev, dist) -> dict:
     """Context parallel on all N ranks of the run: one 131,072-token causal sequence (QH 32, KVH 8,
     d 128), zigzag-sharded, K/V pulled over NVLink inside the attention launches, dK/dV added into
@@ -907,7 +969,7 @@ def run_ring_workload(args, doc_lengths=None, emit=True):
         e[1].record()
         reset()
         e[2].record()
-        bwd(out, lse)
+        grads = bwd(out, lse)
         e[3].record()
         torch.cuda.synchronize()
         t = torch.tensor([e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])], device=dev)
@@ -918,6 +980,9 @@ def run_ring_workload(args, doc_lengths=None, emit=True):
             bwd_ms.append(t[1].item())
     sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
+    torch.backends.cuda.matmul.allow_tf32 = False
+    parity = _ring_workload_parity(rank, world, dev, dist, glens, sizes, starts, q, k, v, dout, out, lse,
+                                   grads[0], cap)
     if rank == 0:
         vis = sum(n * (n + 1) / 2 for n in glens)
         f_flops, b_flops = 4.0 * qh * 128 * vis, 10.0 * qh * 128 * vis
@@ -952,7 +1017,7 @@ def run_ring_workload(args, doc_lengths=None, emit=True):
                                  "nominal_dense_2250": 100.0 * value / world / NOMINAL_BF16_TFLOPS},
             "nvlink": {"kv_ingress_bytes_rank0_fwd": ingress,
                        "achieved_gbs_over_fwd_kernel": ingress / (fm * 1e-3) / 1e9 if world > 1 else 0.0},
-            "gpu_launches": 4 * args.steps, "clocks": clocks,
+            "gpu_launches": 4 * args.steps, "clocks": clocks, "parity": parity,
         }
         if emit:
             print(json.dumps(line), flush=True)
@@ -1104,6 +1169,9 @@ def run_ring_dataset(args) -> None:
             "pct_of_bf16_peak": {f"{peak_kind}_burst": 100.0 * value / world / burst},
             "per_case_tflops_per_gpu": [r["tflops_per_gpu"] for r in records],
             "per_case_placement": [r["config"]["placement"] for r in records],
+            "parity": {"pass": all(r["parity"]["pass"] for r in records), "rule": records[0]["parity"]["rule"],
+                       "worst_err_over_bound": {key: max(r["parity"]["worst_err_over_bound"][key] for r in records)
+                                                for key in ("o", "lse", "dq")}},
             "gpu_launches": 4 * args.steps * len(records), "clocks": records[-1]["clocks"]}), flush=True)
     if world > 1:
         dist.destroy_process_group()
