@@ -447,13 +447,41 @@ def _bound(e_low_precision: float) -> float:
     return 2.0 * max(e_low_precision, 2.0 ** -9)
 
 
-def _ring_workload_parity(rank, world, dev, dist, glens, sizes, starts, q, k, v, dout, out, lse, dq, cap):
+def _key_rows_grads(qf, dof, of, lsef, qpos, kj, vj, kpos_j, low_precision=False):
+    """Checker, plain PyTorch on the GPU: dK and dV of a few key rows ``kj, vj [R, KVH, 128]`` of one
+    causal document from ALL its query rows ``qf, dof, of [T, QH, 128]`` with their log-sum-exp
+    ``lsef [T, QH]`` (the O and LSE rows are the run's own, themselves checked on sampled rows):
+    dV_j = sum_i P_ij dO_i and dK_j = scale * sum_i P_ij (dO_i . v_j - D_i) q_i with
+    P_ij = exp(scale * q_i . k_j - LSE_i) and D_i = dO_i . O_i.  ``low_precision`` computes scores,
+    probabilities, dS and the results in bf16, the yardstick of the acceptance rule."""
+    t, qh = qf.size(0), qf.size(1)
+    kvh = kj.size(1)
+    group = qh // kvh
+    scale = 128 ** -0.5
+    dt = torch.bfloat16 if low_precision else torch.float32      # bf16: products and results rounded too
+    qg = qf.to(dt).view(t, kvh, group, 128)
+    dog = dof.to(dt).view(t, kvh, group, 128)
+    dsum = (dof.float() * of.float()).sum(-1).view(t, kvh, group)
+    lse = lsef.view(t, kvh, group)
+    s_ = torch.einsum("thgd,rhd->thgr", qg, kj.to(dt)).float() * scale
+    p_ = torch.exp(s_ - lse[..., None])
+    p_ = p_.masked_fill((kpos_j[None, :] > qpos[:, None])[:, None, None, :], 0.0)
+    dp = torch.einsum("thgd,rhd->thgr", dog, vj.to(dt)).float()
+    ds = p_ * (dp - dsum[..., None])
+    dv = torch.einsum("thgr,thgd->rhd", p_.to(dt), dog).float()
+    dk = torch.einsum("thgr,thgd->rhd", ds.to(dt), qg).float() * scale
+    return dk, dv
+
+
+def _ring_workload_parity(rank, world, dev, dist, glens, sizes, starts, q, k, v, dout, out, lse, grads, cap):
     """Sampled-row check of a context-parallel run at its full size: for up to three of this
-    rank's documents (largest, smallest, median) a few local query rows, all heads, O / LSE / dQ
-    against plain fp32 PyTorch over the document's K/V gathered from its ring members (checker
-    plumbing: an all_gather of the local K/V).  Bound: 2x the error of the same computation with
-    bf16 scores / probabilities, LSE 1e-3.  The verdict is voted over all ranks."""
-    kvh = k.size(1)
+    rank's documents (largest, smallest, median), all heads, O / LSE / dQ of a few local query
+    rows against plain fp32 PyTorch over the document's K/V, and dK / dV of a few local key rows
+    from all query rows of the document -- the document's tensors are gathered from its ring
+    members (checker plumbing: all_gathers of the local tensors).  Bound: 2x the error of the same
+    computation with bf16 scores / probabilities, LSE 1e-3.  The verdict is voted over all ranks."""
+    dq, dk, dv = grads
+    kvh, qh = k.size(1), q.size(1)
 
     def layout(r):
         lens = [n // g if st <= r < st + g else 0 for n, g, st in zip(glens, sizes, starts)]
@@ -461,52 +489,65 @@ def _ring_workload_parity(rank, world, dev, dist, glens, sizes, starts, q, k, v,
         for n in lens:
             cu.append(cu[-1] + n)
         return lens, cu
-    pad_k = torch.zeros(cap, kvh, 128, dtype=torch.bfloat16, device=dev)
-    pad_v = torch.zeros_like(pad_k)
-    pad_k[:k.size(0)], pad_v[:v.size(0)] = k, v
-    if world > 1:
-        gk = torch.empty(world, cap, kvh, 128, dtype=torch.bfloat16, device=dev)
-        gv = torch.empty_like(gk)
-        dist.all_gather_into_tensor(gk, pad_k)
-        dist.all_gather_into_tensor(gv, pad_v)
-    else:
-        gk, gv = pad_k[None], pad_v[None]
+
+    def gathered(t):
+        """[world, cap, ...] copy of every rank's local rows (zero padded)."""
+        pad = torch.zeros((cap,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+        pad[:t.size(0)] = t
+        if world == 1:
+            return pad[None]
+        full = torch.empty((world,) + tuple(pad.shape), dtype=t.dtype, device=dev)
+        dist.all_gather_into_tensor(full, pad)
+        return full
+    gk, gv, gq, gdo, go = (gathered(t) for t in (k, v, q, dout, out))
+    gl = gathered(lse.t().contiguous())                    # [world, cap, QH]
     lens, cu = layout(rank)
     mine = sorted((d for d in range(len(glens)) if lens[d] > 0), key=lambda d: glens[d])
     picks_d = sorted({mine[0], mine[len(mine) // 2], mine[-1]}) if mine else []
-    worst = {"o": 0.0, "lse": 0.0, "dq": 0.0}
+    worst = {"o": 0.0, "lse": 0.0, "dq": 0.0, "dk": 0.0, "dv": 0.0}
     checked = 0
     for d in picks_d:
         g, st, n = sizes[d], starts[d], lens[d]
-        parts_k, parts_v, parts_pos = [], [], []
-        for m in range(st, st + g):
-            off = layout(m)[1][d]
-            parts_k.append(gk[m, off:off + n])
-            parts_v.append(gv[m, off:off + n])
-            parts_pos.append(_zigzag_positions(g, m - st, n, dev))
-        kf, vf, kpos = torch.cat(parts_k), torch.cat(parts_v), torch.cat(parts_pos)
-        qpos = _zigzag_positions(g, rank - st, n, dev)
+        offs = [layout(m)[1][d] for m in range(st, st + g)]
+
+        def doc(t):
+            return torch.cat([t[m, off:off + n] for m, off in zip(range(st, st + g), offs)])
+        kf, vf = doc(gk), doc(gv)
+        pos = torch.cat([_zigzag_positions(g, m - st, n, dev) for m in range(st, st + g)])
+        mypos = _zigzag_positions(g, rank - st, n, dev)
         rows = torch.tensor(sorted({0, n // 2 - 1, n // 2, n - 1, (104729 * (rank + 3)) % n, (7919 * (d + 5)) % n}),
                             device=dev)
         sel = rows + cu[d]
-        ref_o, ref_l, ref_g = _dense_rows(q[sel], kf, vf, qpos[rows], kpos, dout[sel])
-        low_o, _low_l, low_g = _dense_rows(q[sel], kf, vf, qpos[rows], kpos, dout[sel], low_precision=True)
+        ref_o, ref_l, ref_g = _dense_rows(q[sel], kf, vf, mypos[rows], pos, dout[sel])
+        low_o, _low_l, low_g = _dense_rows(q[sel], kf, vf, mypos[rows], pos, dout[sel], low_precision=True)
         b_o = _bound((low_o - ref_o).abs().max().item())
         b_q = _bound((low_g[0].float() - ref_g[0]).abs().max().item())
         worst["o"] = max(worst["o"], (out[sel].float() - ref_o).abs().max().item() / b_o)
         worst["lse"] = max(worst["lse"], (lse[:, sel] - ref_l).abs().max().item() / 1e-3)
         worst["dq"] = max(worst["dq"], (dq[sel].float() - ref_g[0]).abs().max().item() / b_q)
-        checked += rows.numel()
+        # dK / dV of a few local key rows from every query row of the document
+        krows = torch.tensor(sorted({0, n // 2, n - 1, (15485863 * (rank + 1)) % n}), device=dev)
+        ksel = krows + cu[d]
+        operands = (doc(gq), doc(gdo), doc(go), doc(gl), pos, k[ksel], v[ksel], mypos[krows])
+        ref_dk, ref_dv = _key_rows_grads(*operands)
+        low_dk, low_dv = _key_rows_grads(*operands, low_precision=True)
+        worst["dk"] = max(worst["dk"], (dk[ksel].float() - ref_dk).abs().max().item()
+                          / _bound((low_dk - ref_dk).abs().max().item()))
+        worst["dv"] = max(worst["dv"], (dv[ksel].float() - ref_dv).abs().max().item()
+                          / _bound((low_dv - ref_dv).abs().max().item()))
+        checked += rows.numel() + krows.numel()
     ok = all(x <= 1.0 for x in worst.values())
-    t = torch.tensor([1.0 if ok else 0.0, -worst["o"], -worst["lse"], -worst["dq"], -float(checked)], device=dev)
+    keys = ("o", "lse", "dq", "dk", "dv")
+    t = torch.tensor([1.0 if ok else 0.0, -float(checked)] + [-worst[key] for key in keys], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
     return {"pass": bool(t[0].item() == 1.0),
-            "rule": "O / LSE / dQ of sampled local rows (all heads) of up to three documents per rank against fp32 "
-                    "PyTorch on the GPU; bound 2x the error of the same computation with bf16 scores / "
+            "rule": "up to three documents per rank, all heads: O / LSE / dQ of sampled local query rows against "
+                    "fp32 PyTorch over the document's K/V, dK / dV of sampled local key rows from all query rows "
+                    "of the document; bound 2x the error of the same computation with bf16 scores / "
                     "probabilities, LSE 1e-3; worst ratio over all ranks",
-            "worst_err_over_bound": {"o": -t[1].item(), "lse": -t[2].item(), "dq": -t[3].item()},
-            "rows_checked_max_rank": int(-t[4].item())}
+            "worst_err_over_bound": {key: -t[2 + i].item() for i, key in enumerate(keys)},
+            "rows_checked_max_rank": int(-t[1].item())}
 
 
 def ring_cp_leg(args, rank: int, local_rank: int, world: int, dev, dist) -> dict:
@@ -954,6 +995,95 @@ def run_ring_workload(args, doc_lengths=None, emit=True):
         def reset():
             pass
 
+    if args.ring_impl == "nccl_ring" and world > 1:
+        if varlen:
+            raise SystemExit("--ring-impl nccl_ring is implemented for the single-sequence ring workload")
+        # Second comparison baseline: the classic ring schedule with a library transport.  K/V
+        # shards travel rank to rank with NCCL send/recv (posted before the step's attention so
+        # that they overlap it); each step runs the plain attention kernels on the visiting shard
+        # and merges into the running (out, lse) through the kernel's merge epilogue.  Per step the
+        # two zigzag halves of q are two documents: against the own shard [front | front+back]
+        # with the causal mask, against an earlier rank's shard its front half for both, against
+        # a later rank's shard nothing for the front half and the whole shard for the back half.
+        # Backward: dQ partials are summed in fp32; the fp32 dK/dV of a shard travel with it and
+        # take one more hop home at the end.
+        from min_fa3_demo_b200.min_fa3_op import _call_fwd
+        half = local // 2
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        cu_q2 = torch.tensor([0, half, local], dtype=torch.int32).to(dev)
+        cu_k_own = torch.tensor([0, half, half + local], dtype=torch.int32).to(dev)
+        cu_k_early = torch.tensor([0, half, local], dtype=torch.int32).to(dev)
+        cu_k_late = torch.tensor([0, 0, local], dtype=torch.int32).to(dev)
+        recv_kv = [(torch.empty_like(k), torch.empty_like(v)) for _ in range(2)]
+        recv_g = [(torch.empty(local, kvh, 128, dtype=torch.float32, device=dev),
+                   torch.empty(local, kvh, 128, dtype=torch.float32, device=dev)) for _ in range(2)]
+
+        def step_operands(src, kb, vb):
+            if src == rank:
+                return torch.cat([kb[:half], kb]), torch.cat([vb[:half], vb]), cu_k_own, True, local
+            if src < rank:
+                return (torch.cat([kb[:half], kb[:half]]), torch.cat([vb[:half], vb[:half]]), cu_k_early, False,
+                        half)
+            return kb, vb, cu_k_late, False, local
+
+        def exchange(send, recv):
+            ops = [dist.P2POp(dist.isend, t, nxt) for t in send] + [dist.P2POp(dist.irecv, t, prv) for t in recv]
+            return dist.batch_isend_irecv(ops)
+
+        def fwd():
+            out = torch.zeros_like(q)
+            lse = torch.full((qh, local), float("-inf"), dtype=torch.float32, device=dev)
+            kb, vb = k, v
+            for s in range(world):
+                works = exchange((kb, vb), recv_kv[s & 1]) if s < world - 1 else []
+                k2, v2, cu_k2, causal, max_k = step_operands((rank - s) % world, kb, vb)
+                _call_fwd(q, k2, v2, out, lse, cu_q=cu_q2, cu_k=cu_k2, batch=2, seqlen_q=half, seqlen_k=max_k,
+                          heads_q=qh, heads_k=kvh, is_causal=causal, merge_running=True)
+                for w in works:
+                    w.wait()
+                if s < world - 1:
+                    kb, vb = recv_kv[s & 1]
+            return out, lse
+
+        def bwd(out, lse):
+            dq_acc = torch.zeros(local, qh, 128, dtype=torch.float32, device=dev)
+            gk = torch.zeros(local, kvh, 128, dtype=torch.float32, device=dev)   # dK / dV of the visiting shard
+            gv = torch.zeros_like(gk)
+            kb, vb = k, v
+            g_works = []
+            for s in range(world):
+                src = (rank - s) % world
+                kv_works = exchange((kb, vb), recv_kv[s & 1]) if s < world - 1 else []
+                k2, v2, cu_k2, causal, max_k = step_operands(src, kb, vb)
+                dq_p, dk2, dv2 = min_fa3_op.backward_varlen(dout, q, k2, v2, out, lse, cu_q2, cu_k2, half, max_k,
+                                                            causal)
+                dq_acc += dq_p
+                for w in g_works:          # the visiting shard's gradients so far have arrived
+                    w.wait()
+                if s > 0:
+                    gk, gv = recv_g[(s - 1) & 1]
+                for acc, part in ((gk, dk2), (gv, dv2)):
+                    if src == rank:
+                        acc[:half] += part[:half]
+                        acc += part[half:]
+                    elif src < rank:
+                        acc[:half] += part[:half]
+                        acc[:half] += part[half:]
+                    else:
+                        acc += part
+                g_works = exchange((gk, gv), recv_g[s & 1])      # on to the next holder (last hop: home)
+                for w in kv_works:
+                    w.wait()
+                if s < world - 1:
+                    kb, vb = recv_kv[s & 1]
+            for w in g_works:
+                w.wait()
+            dk_mine, dv_mine = recv_g[(world - 1) & 1]
+            return dq_acc.to(torch.bfloat16), dk_mine.to(torch.bfloat16), dv_mine.to(torch.bfloat16)
+
+        def reset():
+            pass
+
     barrier()
     e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     fwd_ms, bwd_ms = [], []
@@ -982,7 +1112,7 @@ def run_ring_workload(args, doc_lengths=None, emit=True):
     clocks = sampler.stop() if rank == 0 else None
     torch.backends.cuda.matmul.allow_tf32 = False
     parity = _ring_workload_parity(rank, world, dev, dist, glens, sizes, starts, q, k, v, dout, out, lse,
-                                   grads[0], cap)
+                                   grads, cap)
     if rank == 0:
         vis = sum(n * (n + 1) / 2 for n in glens)
         f_flops, b_flops = 4.0 * qh * 128 * vis, 10.0 * qh * 128 * vis
@@ -1006,8 +1136,11 @@ def run_ring_workload(args, doc_lengths=None, emit=True):
                                        f"cp{world} zigzag ring, K/V pulled over NVLink in-kernel")
                        if world > 1 else "single GPU (efficiency baseline)",
                        "copy_ctas": args.ring_comm_sm if world > 1 and args.ring_impl == "fused" else 0,
-                       "exchange": ("in-kernel peer loads (fused)" if args.ring_impl == "fused" else
-                                    "NCCL all_gather of K/V + reduce_scatter of dK/dV (comparison baseline)"),
+                       "exchange": {"fused": "in-kernel peer loads (fused)",
+                                    "allgather": "NCCL all_gather of K/V + reduce_scatter of dK/dV (comparison "
+                                                 "baseline)",
+                                    "nccl_ring": "NCCL send/recv ring of K/V and fp32 dK/dV shards, one attention "
+                                                 "call per ring step (comparison baseline)"}[args.ring_impl],
                        "l2": "inputs larger than L2"},
             "tflops_per_gpu": value / world, "fwd_ms": fm, "bwd_ms": bm,
             "fwd_tflops_per_gpu": f_flops / (fm * 1e-3) / 1e12 / world,
@@ -1171,7 +1304,7 @@ def run_ring_dataset(args) -> None:
             "per_case_placement": [r["config"]["placement"] for r in records],
             "parity": {"pass": all(r["parity"]["pass"] for r in records), "rule": records[0]["parity"]["rule"],
                        "worst_err_over_bound": {key: max(r["parity"]["worst_err_over_bound"][key] for r in records)
-                                                for key in ("o", "lse", "dq")}},
+                                                for key in ("o", "lse", "dq", "dk", "dv")}},
             "gpu_launches": 4 * args.steps * len(records), "clocks": records[-1]["clocks"]}), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -1301,10 +1434,11 @@ def main() -> None:
                         help="bshd workload with the backward's fixed dQ accumulation order (bit-identical repeats)")
     parser.add_argument("--ring-tokens", type=int, default=131072)
     parser.add_argument("--ring-comm-sm", type=int, default=8)
-    parser.add_argument("--ring-impl", choices=("fused", "allgather"), default="fused",
+    parser.add_argument("--ring-impl", choices=("fused", "allgather", "nccl_ring"), default="fused",
                         help="ring workload: fused = K/V pulled inside the attention launch (the product); "
                              "allgather = comparison baseline, NCCL all_gather of K/V + plain varlen attention + "
-                             "NCCL reduce_scatter of dK/dV")
+                             "NCCL reduce_scatter of dK/dV; nccl_ring = second baseline, K/V (and dK/dV) shards passed "
+                             "rank to rank with NCCL send/recv, one plain attention call per ring step")
     parser.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg")
     parser.add_argument("--skip-ring", action="store_true",
                         help="N >= 2: skip the context-parallel leg (131,072-token ring) of the default run")

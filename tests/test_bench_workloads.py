@@ -72,3 +72,20 @@ def test_both_arms_report_the_same_config_record():
     cfg = bench.workload_config(1)
     assert cfg["workload"] == bench.WORKLOAD["name"] and cfg["flops_per_step_per_gpu"] == sum(bench.step_flops())
     assert bench.workload_config(8)["parallelism"].startswith("8 independent")
+
+
+def test_key_row_gradient_checker_equals_autograd():
+    """The bench's dK / dV checker for sampled key rows (from every query row, given O and LSE)
+    is the same function as fp32 autograd through dense causal attention."""
+    import torch
+
+    torch.manual_seed(0)
+    tokens, qh, kvh = 96, 4, 2
+    q, dout = (torch.randn(tokens, qh, 128).to(torch.bfloat16) for _ in range(2))
+    k, v = (torch.randn(tokens, kvh, 128).to(torch.bfloat16) for _ in range(2))
+    pos = torch.arange(tokens)
+    out, lse, grads = bench._dense_rows(q, k, v, pos, pos, dout)
+    rows = torch.tensor([0, 5, 95])
+    dk, dv = bench._key_rows_grads(q, dout, out, lse.t().contiguous(), pos, k[rows], v[rows], pos[rows])
+    torch.testing.assert_close(dk, grads[1][rows], rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(dv, grads[2][rows], rtol=1e-4, atol=1e-4)
