@@ -481,7 +481,6 @@ def _ring_workload_parity(rank, world, dev, dist, glens, sizes, starts, q, k, v,
     members (checker plumbing: all_gathers of the local tensors).  Bound: 2x the error of the same
     computation with bf16 scores / probabilities, LSE 1e-3.  The verdict is voted over all ranks."""
     dq, dk, dv = grads
-    kvh, qh = k.size(1), q.size(1)
 
     def layout(r):
         lens = [n // g if st <= r < st + g else 0 for n, g, st in zip(glens, sizes, starts)]
