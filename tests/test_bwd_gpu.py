@@ -8,7 +8,7 @@ import torch
 
 import min_fa3_op
 from conftest import from_bf16_bits, load_golden
-from gpu_util import assert_within, bound, make_bshd, make_varlen, varlen_bf16_errors
+from gpu_util import assert_lse, assert_within, bound, make_bshd, make_varlen, varlen_bf16_errors
 from oracle import attention_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -69,6 +69,8 @@ def test_bshd_backward_golden(tag, causal):
     ([128, 111, 94, 128, 111, 94], 8, 2),       # S - 17*(i%3), the reference's uneven case
     ([1, 700, 255, 257, 1024, 3], 4, 4),
     ([37] * 40, 2, 2),
+    ([200, 0, 77, 0], 4, 2),                             # empty documents inside and at the end
+    ([0, 128], 2, 2),                                    # ... and in front
 ])
 def test_varlen_backward_vs_oracle(lengths, qh, kvh, causal):
     q, k, v, dout, cu = make_varlen(7 + len(lengths), lengths, qh, kvh)
@@ -83,6 +85,36 @@ def test_varlen_backward_vs_oracle(lengths, qh, kvh, causal):
     assert_within("dQ", dq, rq, e["dq"])
     assert_within("dK", dk, rk, e["dk"])
     assert_within("dV", dv, rv, e["dv"])
+
+
+def test_varlen_document_without_keys():
+    """A document with query rows but no keys: O = 0 and LSE = -inf for its rows (reference:
+    include/min_fa3_epilogue.h:557-631), and they contribute nothing to any gradient."""
+    gen = torch.Generator().manual_seed(23)
+    cu_q = torch.tensor([0, 64, 194, 194 + 300], dtype=torch.int32)
+    cu_k = torch.tensor([0, 0, 130, 130 + 300], dtype=torch.int32)
+    q = torch.randn(494, 4, 128, generator=gen).to(torch.bfloat16)
+    dout = torch.randn(494, 4, 128, generator=gen).to(torch.bfloat16)
+    k = torch.randn(430, 2, 128, generator=gen).to(torch.bfloat16)
+    v = torch.randn(430, 2, 128, generator=gen).to(torch.bfloat16)
+    qc, kc, vc, dc = q.cuda(), k.cuda(), v.cuda(), dout.cuda()
+    out, lse = min_fa3_op.forward_varlen(qc, kc, vc, cu_q.cuda(), cu_k.cuda(), 300, 300, False,
+                                         cu_seqlens_q_host=cu_q, cu_seqlens_k_host=cu_k, return_lse=True)
+    dq, dk, dv = min_fa3_op.backward_varlen(dc, qc, kc, vc, out, lse, cu_q.cuda(), cu_k.cuda(), 300, 300, False)
+    torch.cuda.synchronize()
+    assert bool((out[:64] == 0).all()) and bool(torch.isinf(lse[:, :64]).all()) and bool((lse[:, :64] < 0).all())
+    assert bool((dq[:64] == 0).all())
+    ref_out, ref_lse = orc.varlen_forward(q, k, v, cu_q.tolist(), cu_k.tolist(), False)
+    rq, rk, rv = orc.varlen_backward(q, k, v, dout, cu_q.tolist(), cu_k.tolist(), False)
+    errs = {"o": 0.0, "dq": 0.0, "dk": 0.0, "dv": 0.0}
+    for (qs, qe), (ks, ke) in (((64, 194), (0, 130)), ((194, 494), (130, 430))):
+        e = orc.bf16_attention_error(q[qs:qe][None], k[ks:ke][None], v[ks:ke][None], False, dout[qs:qe][None])
+        errs = {key: max(errs[key], e[key]) for key in errs}
+    assert_within("O", out, ref_out, errs["o"])
+    assert_lse(lse, ref_lse)
+    assert_within("dQ", dq, rq, errs["dq"])
+    assert_within("dK", dk, rk, errs["dk"])
+    assert_within("dV", dv, rv, errs["dv"])
 
 
 @pytest.mark.parametrize("tag,causal", [("full", False), ("causal", True)])

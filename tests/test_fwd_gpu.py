@@ -71,6 +71,8 @@ def test_bshd_forward_golden(tag, causal):
     ([1, 700, 255, 257, 1024, 3], 4, 4),
     ([2048], 2, 1),
     ([37] * 40, 2, 2),                                   # many short documents
+    ([200, 0, 77, 0], 4, 2),                             # empty documents inside and at the end
+    ([0, 128], 2, 2),                                    # ... and in front
 ])
 def test_varlen_forward_vs_oracle(lengths, qh, kvh, causal):
     q, k, v, dout, cu = make_varlen(99 + len(lengths), lengths, qh, kvh)
