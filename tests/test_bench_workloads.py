@@ -89,3 +89,33 @@ def test_key_row_gradient_checker_equals_autograd():
     dk, dv = bench._key_rows_grads(q, dout, out, lse.t().contiguous(), pos, k[rows], v[rows], pos[rows])
     torch.testing.assert_close(dk, grads[1][rows], rtol=1e-4, atol=1e-4)
     torch.testing.assert_close(dv, grads[2][rows], rtol=1e-4, atol=1e-4)
+
+
+def test_ring_parity_checker_accepts_exact_results_and_rejects_a_wrong_document():
+    """The full-size parity record of the ring workloads, run on the CPU for one rank: exact
+    fp32 results of a three-document batch pass with ratios near zero; the same results with one
+    document's output rows swapped for another's fail."""
+    import torch
+
+    torch.manual_seed(1)
+    glens, sizes, starts = [256, 128, 384], [1, 1, 1], [0, 0, 0]
+    qh, kvh, total = 4, 2, 768
+    q, dout = (torch.randn(total, qh, 128).to(torch.bfloat16) for _ in range(2))
+    k, v = (torch.randn(total, kvh, 128).to(torch.bfloat16) for _ in range(2))
+    outs, lses, dqs, dks, dvs = [], [], [], [], []
+    begin = 0
+    for n in glens:
+        pos = torch.arange(n)
+        sl = slice(begin, begin + n)
+        o, l, g = bench._dense_rows(q[sl], k[sl], v[sl], pos, pos, dout[sl])
+        outs.append(o); lses.append(l); dqs.append(g[0]); dks.append(g[1]); dvs.append(g[2])
+        begin += n
+    out, lse = torch.cat(outs), torch.cat(lses, dim=1)
+    grads = (torch.cat(dqs), torch.cat(dks), torch.cat(dvs))
+    dev = torch.device("cpu")
+    good = bench._ring_workload_parity(0, 1, dev, None, glens, sizes, starts, q, k, v, dout, out, lse, grads, total)
+    assert good["pass"] and max(good["worst_err_over_bound"].values()) < 0.05
+    wrong = out.clone()
+    wrong[256:384] = out[0:128]
+    bad = bench._ring_workload_parity(0, 1, dev, None, glens, sizes, starts, q, k, v, dout, wrong, lse, grads, total)
+    assert not bad["pass"] and bad["worst_err_over_bound"]["o"] > 1.0
