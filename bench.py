@@ -495,9 +495,9 @@ def _ring_workload_parity(rank, world, dev, dist, glens, sizes, starts, q, k, v,
         pad[:t.size(0)] = t
         if world == 1:
             return pad[None]
-        full = torch.empty((world,) + tuple(pad.shape), dtype=t.dtype, device=dev)
-        dist.all_gather_into_tensor(full, pad)
-        return full
+        full = torch.empty((world * cap,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+        dist.all_gather_into_tensor(full, pad)          # rank-major concatenation along the rows
+        return full.view((world,) + tuple(pad.shape))
     gk, gv, gq, gdo, go = (gathered(t) for t in (k, v, q, dout, out))
     gl = gathered(lse.t().contiguous())                    # [world, cap, QH]
     lens, cu = layout(rank)

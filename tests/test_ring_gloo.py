@@ -111,3 +111,66 @@ def test_two_rank_placement_sharding_and_exchange(causal):
     assert sum(tokens for _, tokens in results.values()) == sum(LENGTHS)
     for rank, (worst, _) in results.items():
         assert worst < 2e-5, f"rank {rank}: sharded attention differs from the unsharded one by {worst}"
+
+
+# ---------------------------------------------------------------------------------------
+# The benchmark's full-size parity record, on two real ranks: exact results of a mixed batch
+# (one document on a ring of two, one on each rank alone) must pass, and a rank whose output
+# rows of the shared document are in the wrong zigzag order must make the vote fail everywhere.
+# ---------------------------------------------------------------------------------------
+PARITY_DOCS = [(1024, 2, 0), (256, 1, 0), (384, 1, 1)]        # (global length, ring size, ring start)
+
+
+def _parity_worker(rank: int, world: int, port: int, corrupt: bool, results) -> None:
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        dev = torch.device("cpu")
+        gen = torch.Generator().manual_seed(9)
+        parts = {name: [] for name in ("q", "k", "v", "dout", "out", "lse", "dq", "dk", "dv")}
+        for (glen, g, start) in PARITY_DOCS:
+            qg, dg = (torch.randn(glen, QH, D, generator=gen).to(torch.bfloat16) for _ in range(2))
+            kg, vg = (torch.randn(glen, KVH, D, generator=gen).to(torch.bfloat16) for _ in range(2))
+            if not start <= rank < start + g:
+                continue
+            pos = torch.arange(glen)
+            o, l, grads = bench._dense_rows(qg, kg, vg, pos, pos, dg)
+            mine = bench._zigzag_positions(g, rank - start, glen // g, dev)
+            if corrupt and rank == 1 and g == 2:
+                half = mine.numel() // 2
+                o = o.clone()
+                o[mine] = o[torch.cat([mine[half:], mine[:half]])]     # halves of the shard swapped
+            for name, t in (("q", qg), ("k", kg), ("v", vg), ("dout", dg), ("out", o), ("dq", grads[0]),
+                            ("dk", grads[1]), ("dv", grads[2])):
+                parts[name].append(t[mine])
+            parts["lse"].append(l[:, mine])
+        cat = {name: torch.cat(ts, dim=1 if name == "lse" else 0) for name, ts in parts.items()}
+        cap = 1024
+        rec = bench._ring_workload_parity(rank, world, dev, dist, [d[0] for d in PARITY_DOCS],
+                                          [d[1] for d in PARITY_DOCS], [d[2] for d in PARITY_DOCS],
+                                          cat["q"], cat["k"], cat["v"], cat["dout"], cat["out"], cat["lse"],
+                                          (cat["dq"], cat["dk"], cat["dv"]), cap)
+        results[rank] = (rec["pass"], rec["worst_err_over_bound"])
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("corrupt", [False, True])
+def test_bench_parity_record_on_two_ranks(corrupt):
+    world = 2
+    port = _free_port()
+    manager = mp.get_context("spawn").Manager()
+    results = manager.dict()
+    mp.spawn(_parity_worker, args=(world, port, corrupt, results), nprocs=world, join=True)
+    assert set(results.keys()) == {0, 1}
+    for rank, (ok, worst) in results.items():
+        if corrupt:
+            assert not ok and worst["o"] > 1.0, f"rank {rank} accepted a shard in the wrong order: {worst}"
+        else:
+            assert ok and max(worst.values()) < 0.05, f"rank {rank}: {worst}"
