@@ -80,3 +80,34 @@ def test_planner_output_is_accepted_by_the_launcher(lengths, world, causal):
         rc, msg = call(cu=cu, glens=plan.global_lengths, sizes=plan.ring_sizes, starts=plan.ring_starts,
                        world=world, rank=rank, cap=max(cap, 128), causal=int(causal))
         assert rc != _cabi.B2A_ERR_INVALID_ARGUMENT, (rank, msg)
+
+
+# --------------------------------------------------------------------------------------
+# Backward entry point: a sharded document needs copy CTAs for the second pull of the remote
+# K/V -- unless the caller states that the forward's blocks are still in the arena.
+# --------------------------------------------------------------------------------------
+def call_bwd(*, comm, kv_resident):
+    lib = _cabi.load()
+    cu, glens, sizes, starts = (np.asarray(a, dtype=np.int32) for a in ([0, 512], [2048], [4], [0]))
+    a = _cabi.RingBwdArgs()
+    dummy = 0x1000
+    a.dout = a.q = a.out = a.lse = a.dq = a.dk = a.dv = a.arena_k = a.arena_v = a.workspace = dummy
+    for r in range(4):
+        a.peer_k[r] = a.peer_v[r] = a.dk_accum_peer[r] = a.dv_accum_peer[r] = a.completion_peer[r] = dummy
+    a.cu_seqlens_q_host, a.global_seqlens_host, a.ring_sizes_host, a.ring_starts_host = (
+        x.ctypes.data for x in (cu, glens, sizes, starts))
+    a.batch, a.world_size, a.rank, a.rank_kv_capacity = 1, 4, 0, 4096
+    a.total_q = a.local_total_k = 512
+    a.heads_q, a.heads_k, a.head_dim, a.is_causal = 8, 2, 128, 1
+    a.num_comp_sm, a.num_comm_sm, a.kv_resident = 140, comm, kv_resident
+    a.workspace_bytes = 0                  # a valid call stops at the workspace check at the latest
+    rc = lib.b2a_ring_bwd(ctypes.byref(a), None)
+    return rc, lib.b2a_last_error().decode()
+
+
+def test_backward_without_copy_ctas_needs_resident_kv():
+    rc, msg = call_bwd(comm=0, kv_resident=0)
+    assert rc == _cabi.B2A_ERR_INVALID_ARGUMENT and "num_comm_sm must be positive" in msg, (rc, msg)
+    for comm, resident in ((0, 1), (8, 0), (8, 1)):
+        rc, msg = call_bwd(comm=comm, kv_resident=resident)
+        assert rc in (_cabi.B2A_ERR_CUDA, _cabi.B2A_ERR_WORKSPACE_TOO_SMALL, _cabi.B2A_ERR_UNSUPPORTED_DEVICE), (rc, msg)
