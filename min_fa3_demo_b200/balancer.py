@@ -111,14 +111,16 @@ def align_sequence_length(length: int) -> int:
 def _objective(compute: np.ndarray, tokens: np.ndarray, comm: float, avg_c: float, avg_t: float,
                ctol: float, ttol: float, final: bool) -> Tuple[float, float, float, float]:
     """Lexicographic objective: compute-balance violation, token-balance violation (both zero
-    inside the tolerances), then communication volume, then the compute peak.  While documents
+    inside the tolerances), then communication volume, then the compute spread (the larger of
+    peak - average and average - minimum for complete placements, the peak before).  While documents
     are still being placed only overload counts; for complete placements underload counts too."""
     c_over = max(0.0, float(compute.max()) - (1.0 + ctol) * avg_c)
     t_over = max(0.0, float(tokens.max()) - (1.0 + ttol) * avg_t)
     if final:
         c_over = max(c_over, (1.0 - ctol) * avg_c - float(compute.min()))
         t_over = max(t_over, (1.0 - ttol) * avg_t - float(tokens.min()))
-    return (c_over / max(avg_c, 1.0), t_over / max(avg_t, 1.0), comm, float(compute.max()))
+    spread = max(float(compute.max()) - avg_c, avg_c - float(compute.min())) if final else float(compute.max())
+    return (c_over / max(avg_c, 1.0), t_over / max(avg_t, 1.0), comm, spread)
 
 
 def assign_hierarchical_rings(lengths: Sequence[int], world_size: int, is_causal: bool,
@@ -196,7 +198,7 @@ def assign_hierarchical_rings(lengths: Sequence[int], world_size: int, is_causal
                             apply(k, cand_k, +1.0)
                             obj = _objective(compute, tokens, comm[0], avg_c, avg_t, ctol, ttol, True)
                             apply(k, cand_k, -1.0)
-                            if obj[:3] < best_obj[:3]:
+                            if obj < best_obj:
                                 best, best_obj = (cand_i, cand_k), obj
                         apply(i, cand_i, -1.0)
                     if best is not None:
@@ -209,7 +211,8 @@ def assign_hierarchical_rings(lengths: Sequence[int], world_size: int, is_causal
                     apply(k, ck, +1.0)
             return False
 
-        # Local repair: move one document at a time while (violations, communication) improve.
+        # Local repair: move one document at a time while the objective improves (violations,
+        # then communication, then -- at equal communication -- the compute spread).
         moves = 0
         for _ in range(max_repair_iterations):
             improved = False
@@ -222,7 +225,7 @@ def assign_hierarchical_rings(lengths: Sequence[int], world_size: int, is_causal
                     apply(i, cand, +1.0)
                     obj = _objective(compute, tokens, comm[0], avg_c, avg_t, ctol, ttol, True)
                     apply(i, cand, -1.0)
-                    if obj[:3] < best_obj[:3]:
+                    if obj < best_obj:
                         best, best_obj = cand, obj
                 apply(i, best, +1.0)
                 if best != current:
